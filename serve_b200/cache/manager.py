@@ -24,7 +24,7 @@ device to free them, kv_cache_paged.py:72).
 """
 from __future__ import annotations
 
-from dataclasses import dataclass
+from dataclasses import dataclass, field
 from typing import Dict, Hashable, List, Optional, Sequence, Tuple
 
 import numpy as np
@@ -48,6 +48,14 @@ class CacheView:
     writes: bool               # False: reads the cache another execution wrote
     state: object = None       # [max_slots, *state_shape] float32 or None
     window: Optional[int] = None
+    chunk: Optional[int] = None
+    states: Dict[str, object] = field(default_factory=dict)   # named states: [max_slots, *shape] float32 each
+
+    def sub(self, prefix: str) -> "CacheView":
+        """What a part of the layer sees whose state names carry ``prefix``: the same pages, its own states."""
+        n = len(prefix)
+        own = {k[n:]: v for k, v in self.states.items() if k.startswith(prefix)}
+        return CacheView(self.group, self.k, self.v, self.page_size, self.writes, own.get("state"), self.window, self.chunk, own)
 
 
 @dataclass
@@ -56,6 +64,7 @@ class _Group:
     kv_heads: int
     head_dim: int
     window: Optional[int]
+    chunk: Optional[int]
     pool: PagePool
     table: np.ndarray          # [max_slots, max_blocks] int32, -1 where no page
 
@@ -107,11 +116,12 @@ class CacheManager:
             key = need.group_key()
             if key not in key_to_group:
                 key_to_group[key] = len(self.groups)
-                self.groups.append(_Group(key, need.kv_heads, need.head_dim, need.window,
+                self.groups.append(_Group(key, need.kv_heads, need.head_dim, need.window, need.chunk,
                                           PagePool(num_pages[len(self.groups)], len(self.groups)),
                                           np.full((max_slots, self.max_blocks), -1, dtype=np.int32)))
             self._entry_group.append(key_to_group[key])
-        self._windowed = [gi for gi, g in enumerate(self.groups) if g.window is not None]   # groups that give pages back early
+        # groups that give pages back early
+        self._windowed = [gi for gi, g in enumerate(self.groups) if g.window is not None or g.chunk is not None]
         self._free_slots: List[int] = list(range(max_slots - 1, -1, -1))
         self._requests: Dict[Hashable, _Request] = {}
         self._needs = list(needs)
@@ -119,6 +129,7 @@ class CacheManager:
         # device storage
         self._kv: List[Optional[Tuple[object, object]]] = [None] * len(needs)
         self._state: List[object] = [None] * len(needs)
+        self._states: List[Dict[str, object]] = [{} for _ in needs]
         if device is not None:
             import torch
 
@@ -131,6 +142,8 @@ class CacheManager:
                                    torch.zeros(shape, dtype=kv_dtype, device=device))
                 if need.state_shape is not None:
                     self._state[i] = torch.zeros((max_slots,) + tuple(need.state_shape), dtype=torch.float32, device=device)
+                for name, shape in need.states:
+                    self._states[i][name] = torch.zeros((max_slots,) + tuple(shape), dtype=torch.float32, device=device)
 
     # ---- sizes ----------------------------------------------------------
     @staticmethod
@@ -144,13 +157,16 @@ class CacheManager:
         return out
 
     @staticmethod
-    def most_pages_of_a_request(window: Optional[int], page_size: int, length: int, portion: int) -> int:
+    def most_pages_of_a_request(window: Optional[int], page_size: int, length: int, portion: int, chunk: Optional[int] = None) -> int:
         """The most pages one request holds at a time in a group: all of its ``length`` tokens, or, behind a window,
-        what a step of at most ``portion`` new tokens can still read (pages the window has passed were given back)."""
+        what a step of at most ``portion`` new tokens can still read (pages the window has passed were given back).
+        A query that reads only its own block of ``chunk`` positions reaches back fewer than ``chunk`` keys, so such a
+        group counts like one with that window."""
         full = -(-length // page_size)
-        if window is None:
+        reach = min([w for w in (window, chunk) if w is not None], default=None)
+        if reach is None:
             return full
-        return min(full, (window + max(portion, 1) - 2) // page_size + 2)
+        return min(full, (reach + max(portion, 1) - 2) // page_size + 2)
 
     def pool_pages(self) -> List[int]:
         return [g.pool.num_pages for g in self.groups]
@@ -160,7 +176,7 @@ class CacheManager:
 
     def peak_pages(self, length: int, portion: int) -> List[int]:
         """Per group: the most pages a request that grows to ``length`` tokens, at most ``portion`` a step, holds at once."""
-        return [self.most_pages_of_a_request(g.window, self.page_size, length, portion) for g in self.groups]
+        return [self.most_pages_of_a_request(g.window, self.page_size, length, portion, g.chunk) for g in self.groups]
 
     def pages_held(self, rid: Hashable) -> List[int]:
         """Per group: pages the request holds now (what closing it gives back)."""
@@ -185,7 +201,8 @@ class CacheManager:
             kv = self._kv[owner] or (None, None)
             out.append(CacheView(group=self._entry_group[owner] if self._entry_group[owner] is not None else -1,
                                  k=kv[0], v=kv[1], page_size=self.page_size, writes=(src is None),
-                                 state=self._state[owner], window=need_o.window))
+                                 state=self._state[owner], window=need_o.window, chunk=need_o.chunk,
+                                 states=self._states[owner]))
         return out
 
     # ---- requests -------------------------------------------------------
@@ -222,13 +239,18 @@ class CacheManager:
         for st in self._state:
             if st is not None:
                 st[slot].zero_()
+        for named in self._states:
+            for st in named.values():
+                st[slot].zero_()
         return slot
 
     def _first_needed_block(self, g: _Group, length_before: int) -> int:
         """First block a query at position >= length_before can still read."""
-        if g.window is None:
-            return 0
-        first_key = max(0, length_before - g.window + 1)
+        first_key = 0
+        if g.window is not None:
+            first_key = max(0, length_before - g.window + 1)
+        if g.chunk is not None:
+            first_key = max(first_key, (length_before // g.chunk) * g.chunk)
         return first_key // self.page_size
 
     def pages_wanted(self, rid: Hashable, new_len: int) -> List[int]:

@@ -1,6 +1,6 @@
 """Architecture registry and the base of every typed model configuration.
 
-A model folder's ``config.json`` names its architecture in ``architectures[0]``.
+A model folder's ``config.json`` names its architecture in ``architectures[0]`` (or in ``architecture``).
 The registry maps that name to two things: the typed configuration class that
 reads the file's keys, and a function that turns such a configuration into a
 ``ModelSpec`` (the layer-by-layer description the engine builds parts from).
@@ -57,8 +57,10 @@ def lookup_architecture(name: str) -> Tuple[Type[ModelConfig], Callable[[Any], A
 
 def architecture_of(d: Dict[str, Any]) -> str:
     archs = d.get("architectures")
+    if archs is None and isinstance(d.get("architecture"), str):
+        return d["architecture"]               # some files name their one architecture directly
     if not isinstance(archs, (list, tuple)) or len(archs) == 0 or not isinstance(archs[0], str):
-        raise ConfigError("config.json needs a non-empty 'architectures' list naming the model class")
+        raise ConfigError("config.json needs a non-empty 'architectures' list (or an 'architecture' name) naming the model class")
     return archs[0]
 
 

@@ -5,6 +5,10 @@
 // step brings n = cu_q[r+1] - cu_q[r] query tokens at positions
 // kv_len[r] - n .. kv_len[r] - 1; a query at position p attends the cached
 // keys max(0, p - window + 1) .. p of its request (window 0: all of them).
+// Two options for attentions without rotation: ``slopes`` (one float per query
+// head, or null) takes slope_h * (p - key) off every score, and ``chunk`` > 0
+// hides the keys before floor(p / chunk) * chunk (positions count from the start
+// of the sequence, so the blocks do not move with how a prompt was cut).
 // Scores, running maximum, sum and the output accumulator are float; the
 // online-softmax recurrences are those of serve/kernels/attn_prefill.py:58-72,
 // in base e. Compile with -DSB_HEAD_DIM=<multiple of 16>.
@@ -30,7 +34,8 @@ template <typename T>
 __global__ void __launch_bounds__(THREADS) attention_simt_kernel(
     const T* __restrict__ qkv, int q_stride, const T* __restrict__ kc, const T* __restrict__ vc,  // caches [P, Hkv, ps, D]
     const int* __restrict__ block_table, int bt_width, const int* __restrict__ cu_q, const int* __restrict__ kv_len, int H,
-    int Hkv, int ps, int num_pages, float scale, int window, T* __restrict__ out, int decode_apart) {
+    int Hkv, int ps, int num_pages, float scale, int window, T* __restrict__ out, int decode_apart,
+    const float* __restrict__ slopes, int chunk) {
   extern __shared__ float smem[];
   float* Qs = smem;                 // [BM][D]
   float* Ks = Qs + BM * D;          // [BN][KSTRIDE]
@@ -56,8 +61,11 @@ __global__ void __launch_bounds__(THREADS) attention_simt_kernel(
   const int pi = p0 + m0 + i;                       // this thread's query position
   const bool row_ok = (m0 + i) < qn;
   const int first_pos = p0 + m0, last_pos = p0 + min(m0 + BM, qn) - 1;
-  const int lo = window > 0 ? max(0, first_pos - window + 1) : 0;
+  int lo = window > 0 ? max(0, first_pos - window + 1) : 0;
+  if (chunk > 0) lo = max(lo, (first_pos / chunk) * chunk);
   const int hi = last_pos + 1;                      // exclusive; <= L
+  const float slope = slopes ? slopes[h] : 0.f;
+  const int chunk_lo = chunk > 0 ? (pi / chunk) * chunk : 0;
 
   float m_run = -INFINITY, l_run = 0.f;
   float acc[D / 8];
@@ -97,8 +105,8 @@ __global__ void __launch_bounds__(THREADS) attention_simt_kernel(
 #pragma unroll
     for (int c = 0; c < BN / 8; ++c) {
       const int key = kt + jj + 8 * c;
-      const bool ok = row_ok && key <= pi && (window <= 0 || key > pi - window);
-      s[c] = ok ? s[c] * scale : -INFINITY;
+      const bool ok = row_ok && key <= pi && key >= chunk_lo && (window <= 0 || key > pi - window);
+      s[c] = ok ? s[c] * scale - slope * (float)(pi - key) : -INFINITY;
       tmax = fmaxf(tmax, s[c]);
     }
     tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, 1));
@@ -178,7 +186,7 @@ template <typename T>
 __global__ void __launch_bounds__(DEC_WARPS * 32) attention_simt_decode_kernel(
     const T* __restrict__ qkv, int q_stride, const T* __restrict__ kc, const T* __restrict__ vc,
     const int* __restrict__ block_table, int bt_width, const int* __restrict__ cu_q, const int* __restrict__ kv_len, int H,
-    int Hkv, int ps, int num_pages, float scale, int window, T* __restrict__ out) {
+    int Hkv, int ps, int num_pages, float scale, int window, T* __restrict__ out, const float* __restrict__ slopes, int chunk) {
   extern __shared__ float smem[];
   float* Qs = smem;                                        // [16][D]
   float* Om = Qs + 16 * D;                                 // [DEC_STREAMS][DEC_ROWS][LPK * EPL]
@@ -202,11 +210,14 @@ __global__ void __launch_bounds__(DEC_WARPS * 32) attention_simt_decode_kernel(
   const int* bt = block_table + (size_t)r * bt_width;
   for (int m0 = 0; m0 < M; m0 += DEC_ROWS) {
     float q[DEC_ROWS][EPL], acc[DEC_ROWS][EPL], m_run[DEC_ROWS], l_run[DEC_ROWS];
-    int pos[DEC_ROWS];
+    int pos[DEC_ROWS], first_key[DEC_ROWS];
+    float slope[DEC_ROWS];
 #pragma unroll
     for (int i = 0; i < DEC_ROWS; ++i) {
       const bool valid = m0 + i < M;
       pos[i] = valid ? p0 + (m0 + i) / G : -1;
+      first_key[i] = (valid && chunk > 0) ? (pos[i] / chunk) * chunk : 0;
+      slope[i] = (valid && slopes) ? slopes[hk * G + (m0 + i) % G] : 0.f;
       m_run[i] = -INFINITY;
       l_run[i] = 0.f;
 #pragma unroll
@@ -216,7 +227,8 @@ __global__ void __launch_bounds__(DEC_WARPS * 32) attention_simt_decode_kernel(
       }
     }
     const int last_row = min(m0 + DEC_ROWS, M) - 1;
-    const int lo = window > 0 ? max(0, p0 + m0 / G - window + 1) : 0;
+    int lo = window > 0 ? max(0, p0 + m0 / G - window + 1) : 0;
+    if (chunk > 0) lo = max(lo, ((p0 + m0 / G) / chunk) * chunk);
     const int hi = p0 + last_row / G + 1;             // exclusive; <= L
     // this stream's keys: lo + stream, then DEC_STREAMS further on; the next key's loads go out before this key's sums
     auto locate = [&](int key, size_t& off) -> bool {
@@ -250,8 +262,9 @@ __global__ void __launch_bounds__(DEC_WARPS * 32) attention_simt_decode_kernel(
         for (int e = 0; e < EPL; ++e) sc += q[i][e] * kv[e];
 #pragma unroll
         for (int o = LPK / 2; o > 0; o >>= 1) sc += __shfl_xor_sync(0xffffffffu, sc, o);
-        const bool ok = this_there && this_key <= pos[i] && (window <= 0 || this_key > pos[i] - window);
+        const bool ok = this_there && this_key <= pos[i] && this_key >= first_key[i] && (window <= 0 || this_key > pos[i] - window);
         if (ok) {
+          sc -= slope[i] * (float)(pos[i] - this_key);
           const float m_new = fmaxf(m_run[i], sc);
           const float alpha = (m_run[i] == -INFINITY) ? 0.f : expf(m_run[i] - m_new);
           const float pr = expf(sc - m_new);
@@ -292,9 +305,12 @@ __global__ void __launch_bounds__(DEC_WARPS * 32) attention_simt_decode_kernel(
 
 SB_EXPORT int sb_attention_simt_head_dim() { return D; }
 
-SB_EXPORT int sb_attention_simt(const void* qkv, int q_stride, const void* kc, const void* vc, const int* block_table, int bt_width,
-                                const int* cu_q, const int* kv_len, int H, int Hkv, int ps, int num_pages, float scale, int window,
-                                void* out, int n_rows, int max_q, int dtype, cudaStream_t stream) {
+// As sb_attention_simt below, with the two options of scores that depend on distance: ``slopes`` (float [H] or null)
+// and ``chunk`` (0: none).
+SB_EXPORT int sb_attention_simt_biased(const void* qkv, int q_stride, const void* kc, const void* vc, const int* block_table,
+                                       int bt_width, const int* cu_q, const int* kv_len, int H, int Hkv, int ps, int num_pages,
+                                       float scale, int window, void* out, int n_rows, int max_q, int dtype, const float* slopes,
+                                       int chunk, cudaStream_t stream) {
   if (n_rows <= 0 || max_q <= 0) return 0;
   if (H <= 0 || Hkv <= 0 || H % Hkv || ps <= 0 || bt_width <= 0) return SB_ERR_SHAPE;
   if (H > 65535 || n_rows > 65535) return SB_ERR_LIMIT;
@@ -312,7 +328,7 @@ SB_EXPORT int sb_attention_simt(const void* qkv, int q_stride, const void* kc, c
       auto k = attention_simt_kernel<float>;
       if (smem > 48 * 1024) cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
       k<<<grid, THREADS, smem, stream>>>((const float*)qkv, q_stride, (const float*)kc, (const float*)vc, block_table, bt_width, cu_q,
-                                         kv_len, H, Hkv, ps, num_pages, scale, window, (float*)out, decode_shape ? 1 : 0);
+                                         kv_len, H, Hkv, ps, num_pages, scale, window, (float*)out, decode_shape ? 1 : 0, slopes, chunk);
       SB_LAUNCH_CHECK();
     }
     if (decode_shape) {
@@ -322,14 +338,14 @@ SB_EXPORT int sb_attention_simt(const void* qkv, int q_stride, const void* kc, c
     if (decode_shape)
       attention_simt_decode_kernel<float><<<dgrid, DEC_WARPS * 32, dsmem, stream>>>(
           (const float*)qkv, q_stride, (const float*)kc, (const float*)vc, block_table, bt_width, cu_q, kv_len, H, Hkv, ps, num_pages,
-          scale, window, (float*)out);
+          scale, window, (float*)out, slopes, chunk);
   } else if (dtype == SB_DTYPE_BF16) {
     if (tiles_needed) {
       auto k = attention_simt_kernel<__nv_bfloat16>;
       if (smem > 48 * 1024) cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
       k<<<grid, THREADS, smem, stream>>>((const __nv_bfloat16*)qkv, q_stride, (const __nv_bfloat16*)kc, (const __nv_bfloat16*)vc,
                                          block_table, bt_width, cu_q, kv_len, H, Hkv, ps, num_pages, scale, window,
-                                         (__nv_bfloat16*)out, decode_shape ? 1 : 0);
+                                         (__nv_bfloat16*)out, decode_shape ? 1 : 0, slopes, chunk);
       SB_LAUNCH_CHECK();
     }
     if (decode_shape) {
@@ -339,10 +355,17 @@ SB_EXPORT int sb_attention_simt(const void* qkv, int q_stride, const void* kc, c
     if (decode_shape)
       attention_simt_decode_kernel<__nv_bfloat16><<<dgrid, DEC_WARPS * 32, dsmem, stream>>>(
           (const __nv_bfloat16*)qkv, q_stride, (const __nv_bfloat16*)kc, (const __nv_bfloat16*)vc, block_table, bt_width, cu_q, kv_len, H,
-          Hkv, ps, num_pages, scale, window, (__nv_bfloat16*)out);
+          Hkv, ps, num_pages, scale, window, (__nv_bfloat16*)out, slopes, chunk);
   } else {
     return SB_ERR_DTYPE;
   }
   SB_LAUNCH_CHECK();
   return 0;
+}
+
+SB_EXPORT int sb_attention_simt(const void* qkv, int q_stride, const void* kc, const void* vc, const int* block_table, int bt_width,
+                                const int* cu_q, const int* kv_len, int H, int Hkv, int ps, int num_pages, float scale, int window,
+                                void* out, int n_rows, int max_q, int dtype, cudaStream_t stream) {
+  return sb_attention_simt_biased(qkv, q_stride, kc, vc, block_table, bt_width, cu_q, kv_len, H, Hkv, ps, num_pages, scale, window, out,
+                                  n_rows, max_q, dtype, nullptr, 0, stream);
 }

@@ -29,9 +29,12 @@ int ensure_handle(int dev) {
 }
 }  // namespace
 
-SB_EXPORT int sb_linear(const void* a, const void* w, void* out, int M, int N, int K, int in_dtype, int out_dtype,
-                        cudaStream_t stream) {
+// As sb_linear, for operands that are column slices of wider buffers: the rows of a are lda elements apart and
+// those of out ldc elements (w is always whole, its rows K apart).
+SB_EXPORT int sb_linear_ld(const void* a, int lda, const void* w, void* out, int ldc, int M, int N, int K, int in_dtype, int out_dtype,
+                           cudaStream_t stream) {
   if (M <= 0 || N <= 0) return 0;
+  if (lda < K || ldc < N) return SB_ERR_SHAPE;
   if (K <= 0) return SB_ERR_SHAPE;
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess) return -103;
@@ -54,8 +57,13 @@ SB_EXPORT int sb_linear(const void* a, const void* w, void* out, int M, int N, i
     return SB_ERR_DTYPE;
   }
   // row-major out[M,N] is column-major [N,M]: out^T = w (as op T of col-major [K,N]) * a^T (col-major [K,M])
-  cublasStatus_t st = cublasGemmEx(h, CUBLAS_OP_T, CUBLAS_OP_N, N, M, K, &alpha, w, in_t, K, a, in_t, K, &beta, out, out_t, N, comp,
+  cublasStatus_t st = cublasGemmEx(h, CUBLAS_OP_T, CUBLAS_OP_N, N, M, K, &alpha, w, in_t, K, a, in_t, lda, &beta, out, out_t, ldc, comp,
                                    CUBLAS_GEMM_DEFAULT);
   if (st != CUBLAS_STATUS_SUCCESS) return -200 - (int)st;
   return 0;
+}
+
+SB_EXPORT int sb_linear(const void* a, const void* w, void* out, int M, int N, int K, int in_dtype, int out_dtype,
+                        cudaStream_t stream) {
+  return sb_linear_ld(a, K, w, out, N, M, N, K, in_dtype, out_dtype, stream);
 }

@@ -92,7 +92,7 @@ class Engine:
             # the share is what the memory fraction pays for, at most all of it.
             keys = CacheManager.group_keys(needs)
             per_page = CacheManager.bytes_per_page(needs, ec.page_size, self.dtype.itemsize)
-            most = [ec.max_slots * CacheManager.most_pages_of_a_request(key[2], ec.page_size, self.max_context, ec.max_tokens_per_step)
+            most = [ec.max_slots * CacheManager.most_pages_of_a_request(key[2], ec.page_size, self.max_context, ec.max_tokens_per_step, key[3])
                     for key in keys]
             share = 1.0
             if self.rt.device.type == "cuda" and keys:

@@ -71,6 +71,11 @@ def core_jobs():
     ]
 
 
+def sequence_job():
+    """Kernels of the mixers with recurrent state and of routed experts (built when a model first asks for them)."""
+    return {"name": "sb_seq", "sources": ["sequence_ops.cu", "routed_experts.cu"]}
+
+
 def attention_job(head_dim: int):
     return {"name": f"sb_attention_hd{head_dim}", "sources": ["attention_simt.cu", "attention_mma.cu", "attention_tc.cu"],
             "defines": [f"SB_HEAD_DIM={head_dim}"]}
@@ -108,7 +113,8 @@ class LayerRunPlan:
 
 def all_jobs():
     """Every library the engine can ask for (the build check compiles them all)."""
-    return core_jobs() + [attention_job(d) for d in SUPPORTED_HEAD_DIMS] + [layer_run_job(d) for d in LAYER_RUN_HEAD_DIMS]
+    return (core_jobs() + [sequence_job()] + [attention_job(d) for d in SUPPORTED_HEAD_DIMS]
+            + [layer_run_job(d) for d in LAYER_RUN_HEAD_DIMS])
 
 
 class CudaKernels:
@@ -151,6 +157,7 @@ class CudaKernels:
         # Llama-3.2-1B shape it is slower than the chain of separate kernels (about 80 us a layer against 42), so it is
         # off unless asked for (tests, and SERVE_B200_LAYER_RUNS=1 for measurements).
         self.use_layer_runs = os.environ.get("SERVE_B200_LAYER_RUNS", "0") == "1"
+        self._seq = None                     # the library of sequence_job(), loaded at first use
         self._stack: Dict[int, ctypes.CDLL] = {}
         self._stack_sync = None              # two counters of the layer-run kernel's grid barrier (zero between launches)
         self._stack_partials = None
@@ -251,6 +258,14 @@ class CudaKernels:
         if a.dtype != w.dtype or a.shape[1] != w.shape[1] or out.shape[0] != a.shape[0] or out.shape[1] != w.shape[0]:
             raise KernelError(f"linear: a {tuple(a.shape)} {a.dtype}, w {tuple(w.shape)} {w.dtype}, out {tuple(out.shape)} do not fit")
         m, n, k = a.shape[0], w.shape[0], a.shape[1]
+        if a.stride(0) != k or out.stride(0) != n:
+            # a column slice of a wider buffer on either side: the library takes the row strides
+            if a.stride(1) != 1 or out.stride(1) != 1:
+                raise KernelError("linear: operands must be contiguous along their rows")
+            self.library_calls += 1
+            _check(self._gemm.sb_linear_ld(_p(a), a.stride(0), _p(w), _p(out), out.stride(0), m, n, k, _DT[a.dtype], _DT[out.dtype],
+                                           self._s()), "linear")
+            return
         key = (a.dtype, out.dtype, m, n, k, self.use_skinny_linear, self.use_tcgen05, self.TCGEN05_MIN_TILES, self.tcgen05_for_plain_products, 0)
         route = self._routes.get(key)
         if route is None:
@@ -362,8 +377,18 @@ class CudaKernels:
                               k_cache, v_cache, block_table, page_size, write_cache)
 
     def attention(self, qkv, k_cache, v_cache, block_table, cu_q, kv_len, token_row, positions, heads, kv_heads, head_dim,
-                  page_size, scale, window, out, shape) -> None:
+                  page_size, scale, window, out, shape, slopes=None, chunk: int = 0) -> None:
+        """``slopes`` (float [heads]): slope_h * distance is taken off every score; ``chunk`` > 0: a query sees only the keys of
+        its own block of ``chunk`` positions. Both run on the plain-arithmetic kernel, in either dtype."""
         lib = self._attention_lib(head_dim)
+        if slopes is not None or chunk:
+            group = heads // kv_heads
+            self.launches += (1 if group <= 16 else 0) + (1 if group > 16 or shape.max_q * group > 16 else 0)
+            _check(lib.sb_attention_simt_biased(
+                _p(qkv), qkv.stride(0), _p(k_cache), _p(v_cache), _p(block_table), block_table.shape[1], _p(cu_q), _p(kv_len),
+                heads, kv_heads, page_size, k_cache.shape[0], ctypes.c_float(scale), window, _p(out), shape.rows, shape.max_q,
+                _DT[qkv.dtype], _p(slopes), int(chunk), self._s()), "attention with distance bias")
+            return
         if qkv.dtype == torch.bfloat16 and not self.force_simt_attention:
             return self._attention_mma(lib, qkv, k_cache, v_cache, block_table, cu_q, kv_len, heads, kv_heads, head_dim,
                                        page_size, scale, window, out, shape)
@@ -579,6 +604,95 @@ class CudaKernels:
             _p(qkv), _p(attn), _p(inter), _p(partials), _p(tickets), num_splits, _p(self._stack_sync), _p(self.errors_tensor()),
             plan.blocks, _p(self.layer_run_timing), self._s()), "layers of a decoding step")
         return x, delta_down
+
+    # ---- mixers with recurrent state, routed experts ------------------------------------------------------------------
+    def _seq_lib(self):
+        if self._seq is None:
+            job = sequence_job()
+            job["verbose"] = self._verbose
+            path = build.build_library(**job)
+            self.paths[job["name"]] = path
+            self._seq = ctypes.CDLL(path)
+        return self._seq
+
+    def causal_conv(self, x, weight, bias, state, ctx, out, activation: str = "none", residual: bool = False) -> None:
+        """out[t] = act(bias + sum_j weight[:, j] * x[t - taps + 1 + j] (+ x[t])) per channel, over each request's own tokens;
+        the taps - 1 inputs before a portion come from ``state`` [slots, taps - 1, C] (float), which then takes the portion's
+        last ones. x and out may be column slices (row strides are passed on)."""
+        c, taps = weight.shape
+        self.launches += 1 if (ctx.shape.pure_decode or taps == 1) else 2
+        _check(self._seq_lib().sb_causal_conv(
+            _p(x), x.stride(0), _p(weight), _p(bias), _p(state), _p(ctx.slots), _p(ctx.cu_q), _p(ctx.token_row), _p(out), out.stride(0),
+            c, taps, {"none": 0, "silu": 1}[activation], 1 if residual else 0, x.shape[0], ctx.shape.rows,
+            1 if ctx.shape.pure_decode else 0, _DT[x.dtype], self._s()), "short convolution")
+
+    def linear_recurrence(self, mode: str, q, k, v, state, ctx, out, heads: int, qk_heads: int, dk: int, dv: int, aux=None, rate=None,
+                          decay=None, a_log=None, dt_bias=None, d_skip=None, q_scale: float = 1.0) -> None:
+        """One matrix state [dk, dv] per (request, head), walked over the step's tokens: see csrc/sequence_ops.cu.
+        mode "decay": S = decay_h S + k v^T with silu on q, k, v; "ssm": S = exp(-exp(a_log) dt) S + dt k v^T, dt =
+        softplus(aux + dt_bias), o += d_skip v; "delta": S = g S, S += k (beta (v - S^T k))^T with g = exp(-exp(a_log)
+        softplus(rate + dt_bias)), beta = sigmoid(aux), q and k made unit vectors. out: float [T, heads * dv]."""
+        par = a_log if a_log is not None else None
+        self.launches += 1
+        _check(self._seq_lib().sb_linear_recurrence(
+            {"decay": 0, "ssm": 1, "delta": 2}[mode], _p(q), q.stride(0), _p(k), k.stride(0), _p(v), v.stride(0),
+            _p(aux), aux.stride(0) if aux is not None else 0, _p(rate), rate.stride(0) if rate is not None else 0, _p(decay),
+            _p(a_log), _p(dt_bias), _p(d_skip), _DT[par.dtype] if par is not None else 0, _p(state), _p(ctx.slots), _p(ctx.cu_q),
+            _p(out), out.stride(0), heads, qk_heads, dk, dv, ctypes.c_float(q_scale), ctx.shape.rows, _DT[v.dtype], self._s()),
+            "linear recurrence")
+
+    def gated_norm(self, y, out, groups: int = 0, eps: float = 0.0, weight=None, gate=None, gate_act: str = "sigmoid",
+                   gate_first: bool = False, scale: float = 1.0) -> None:
+        """out = scale * [gate *] rms_groups([gate *] y) * weight: y float [T, C]; ``groups`` equal parts of a row are each divided
+        by their root mean square (0: no division); y is float or of out's type; weight [w] with w dividing C; gate [T, g] with g dividing C."""
+        self.launches += 1
+        _check(self._seq_lib().sb_gated_norm(
+            _p(y), _DT[y.dtype], y.stride(0), _p(gate), gate.stride(0) if gate is not None else 0, gate.shape[1] if gate is not None else 0,
+            {"sigmoid": 0, "silu": 1}[gate_act], 1 if gate_first else 0, _p(weight), _DT[weight.dtype] if weight is not None else 0,
+            weight.shape[0] if weight is not None else 0, _p(out), out.stride(0), y.shape[0], y.shape[1], groups, ctypes.c_float(eps),
+            ctypes.c_float(scale), _DT[out.dtype], self._s()), "norm and gate")
+
+    def kv_norm_cache_write(self, qkv, positions, token_row, heads, kv_heads, head_dim, norm_dim, eps, k_cache, v_cache, block_table,
+                            page_size) -> None:
+        """Keys and values of the step's tokens into their pages, without rotation; with norm_dim > 0 each value head is first
+        divided by the root mean square of its first norm_dim elements."""
+        self.launches += 1
+        _check(self._seq_lib().sb_kv_norm_cache_write(
+            _p(qkv), qkv.stride(0), _p(positions), _p(token_row), heads, kv_heads, head_dim, norm_dim, ctypes.c_float(eps), _p(k_cache),
+            _p(v_cache), _p(block_table), block_table.shape[1], page_size, k_cache.shape[0], qkv.shape[0], _p(self.errors_tensor()),
+            _DT[qkv.dtype], self._s()), "cache write with value norm")
+
+    def routed_experts(self, h, logits, w_gate_up, w_down, top: int, out, score: str = "sigmoid", renormalise: bool = False,
+                       scale_input: bool = True, activation: str = "clamped_swish", limit: float = 0.0, alpha: float = 1.702) -> None:
+        """out[t] = sum over the ``top`` best experts e of expert_e(w_e * h[t]) (or w_e * expert_e(h[t])): logits float [T, E],
+        w_gate_up [E, 2 ff, K], w_down [E, N, ff]."""
+        lib = self._seq_lib()
+        t, e = logits.shape
+        ff, n, k = w_down.shape[2], w_down.shape[1], h.shape[1]
+        pairs = t * top
+        dev = h.device
+        max_tiles = pairs // lib.sb_moe_tile_rows() + min(e, pairs)
+        ints = torch.empty(2 * pairs + e + 1 + 2 * max_tiles + 1, dtype=torch.int32, device=dev)
+        idx, order = ints[:pairs], ints[pairs: 2 * pairs]
+        offsets = ints[2 * pairs: 2 * pairs + e + 1]
+        tiles = ints[2 * pairs + e + 1: 2 * pairs + e + 1 + 2 * max_tiles]
+        n_tiles = ints[-1:]
+        wts = torch.empty(pairs, dtype=torch.float32, device=dev)
+        s = self._s()
+        self.launches += 4
+        _check(lib.sb_moe_route(_p(logits), e, top, {"sigmoid": 0, "softmax": 1}[score], 1 if renormalise else 0, t, _p(idx), _p(wts), s),
+               "expert choice")
+        _check(lib.sb_moe_sort(_p(idx), pairs, e, _p(offsets), _p(order), _p(tiles), _p(n_tiles), s), "grouping by expert")
+        act = torch.empty((pairs, ff), dtype=h.dtype, device=dev)
+        _check(lib.sb_moe_gate_up(_p(h), h.stride(0), _p(w_gate_up), _p(order), _p(offsets), _p(tiles), _p(n_tiles), _p(wts), top, pairs,
+                                  e, k, ff, 1 if scale_input else 0, {"swiglu": 0, "clamped_swish": 1}[activation],
+                                  ctypes.c_float(limit), ctypes.c_float(alpha), _p(act), _DT[h.dtype], s), "experts, gate and up")
+        parts = out if top == 1 else torch.empty((pairs, n), dtype=torch.float32, device=dev)
+        _check(lib.sb_moe_down(_p(act), _p(w_down), _p(order), _p(offsets), _p(tiles), _p(n_tiles), _p(wts), pairs, e, ff, n,
+                               0 if scale_input else 1, _p(parts), _DT[h.dtype], _DT[parts.dtype], s), "experts, down")
+        if top > 1:
+            self.launches += 1
+            _check(lib.sb_moe_combine(_p(parts), top, t, n, _p(out), _DT[out.dtype], s), "sum over a token's experts")
 
     def sample(self, logits, temperature, req_ids, tok_index, seed, out, slots=None, last_token=None) -> None:
         self.launches += 1

@@ -1,6 +1,7 @@
 """Parts a layer is put together from; importing this package registers the built-in ones."""
 from .base import (  # noqa: F401
-    Block, CacheNeed, FeedForward, Mixer, Norm, Part, PositionEncoding, TensorDecl,
+    Block, CacheNeed, FeedForward, Mixer, Norm, Part, PositionEncoding, SequenceFilter, TensorDecl,
     build_part, register_part, registered,
 )
 from . import norm, rotary, attention, feed_forward, block, embedding  # noqa: F401
+from . import short_conv, gated_norm, linear_recurrence, biased_attention, parallel, routed_experts  # noqa: F401,E402

@@ -38,16 +38,21 @@ class TensorDecl:
 class CacheNeed:
     """What one execution of a mixer wants from the cache manager.
 
-    A mixer with keys and values in pages gives kv_heads/head_dim (and a window
-    if only the last ``window`` keys are ever read). A mixer with per-request
-    state of fixed size gives ``state_shape`` (elements of float32 per request).
-    Either may be absent.
+    A mixer with keys and values in pages gives kv_heads/head_dim, a window if
+    only the last ``window`` keys are ever read, and ``chunk`` if a query only
+    reads the keys of its own block of ``chunk`` positions (counted from the
+    start of the sequence). A mixer with per-request state of fixed size gives
+    ``state_shape`` (elements of float32 per request); a layer with several
+    such states (a recurrence and the tails of its convolutions, say) names
+    them in ``states``, a tuple of (name, shape) pairs. Any may be absent.
     """
 
     kv_heads: int = 0
     head_dim: int = 0
     window: Optional[int] = None
     state_shape: Optional[Tuple[int, ...]] = None
+    chunk: Optional[int] = None
+    states: Tuple[Tuple[str, Tuple[int, ...]], ...] = ()
 
     @property
     def has_pages(self) -> bool:
@@ -55,7 +60,26 @@ class CacheNeed:
 
     def group_key(self) -> Tuple:
         """Executions with equal keys share page geometry, a pool and block tables."""
-        return (self.kv_heads, self.head_dim, self.window)
+        return (self.kv_heads, self.head_dim, self.window, self.chunk)
+
+    @staticmethod
+    def merged(needs: "List[Tuple[str, Optional[CacheNeed]]]") -> "Optional[CacheNeed]":
+        """One need out of those of several parts of a layer, each with the prefix its state names get. At most
+        one of them may want pages."""
+        paged = [n for _, n in needs if n is not None and n.has_pages]
+        if len(paged) > 1:
+            raise ValueError("a layer can own the pages of one mixer only")
+        states = []
+        for prefix, n in needs:
+            if n is None:
+                continue
+            if n.state_shape is not None:
+                states.append((prefix + "state", tuple(n.state_shape)))
+            states.extend((prefix + name, tuple(shape)) for name, shape in n.states)
+        if not paged and not states:
+            return None
+        p = paged[0] if paged else CacheNeed()
+        return CacheNeed(p.kv_heads, p.head_dim, p.window, None, p.chunk, tuple(states))
 
 
 class Part:
@@ -80,6 +104,17 @@ class Part:
 class Mixer(Part):
     def cache_need(self) -> Optional[CacheNeed]:
         return None
+
+    # A mixer whose last step is a plain output projection may offer it apart: ``mix_into`` writes what the projection
+    # reads (times ``scale``) into ``out``, a [T, mixed_size] column slice, and ``output_weight`` is the projection's
+    # [hidden, mixed_size] matrix. An arrangement of several such mixers then projects all of them with one product.
+    mixed_size: Optional[int] = None
+
+    def mix_into(self, h, ctx, cache, out, scale: float = 1.0) -> None:
+        raise NotImplementedError
+
+    def output_weight(self):
+        raise NotImplementedError
 
     def forward(self, h, ctx, cache):
         """h: [T, hidden] activations -> [T, hidden] activations (the residual delta).
@@ -110,6 +145,17 @@ class PositionEncoding(Part):
     """Held by a mixer; describes how positions enter queries and keys."""
 
 
+class SequenceFilter(Part):
+    """A filter over time on the input of a sub-layer or inside a mixer (a short convolution): it may keep a state."""
+
+    def cache_need(self) -> Optional[CacheNeed]:
+        return None
+
+    def forward(self, x, ctx, cache, out=None, prefix: str = ""):
+        """x [T, C] -> [T, C]; ``cache.states[prefix + name]`` holds this filter's state."""
+        raise NotImplementedError
+
+
 class Block(Part):
     """An arrangement of parts around the residual stream.
 
@@ -123,17 +169,21 @@ class Block(Part):
     """
 
     wants: Dict[str, str] = {}
+    optional: Tuple[str, ...] = ()      # names of ``wants`` that a layer may leave out (the attribute is then None)
 
     def __init__(self, spec: PartSpec, runtime, parts: Optional[Dict[str, PartSpec]] = None):
         super().__init__(spec, runtime)
         given = dict(parts or {})
-        missing = [n for n in self.wants if n not in given]
+        missing = [n for n in self.wants if n not in given and n not in self.optional]
         extra = [n for n in given if n not in self.wants]
         if missing or extra:
             raise KeyError(f"block {spec.kind!r} arranges the parts {sorted(self.wants)}; the layer description "
                            f"lacks {sorted(missing)} and has {sorted(extra)} beyond them")
         self._built = []
         for name, family in self.wants.items():
+            if name not in given:
+                setattr(self, name, None)
+                continue
             part = build_part(family, given[name], runtime)
             setattr(self, name, part)
             self._built.append(part)
@@ -155,6 +205,7 @@ _REGISTRIES: Dict[str, Dict[str, Callable]] = {
     "feed_forward": {},
     "norm": {},
     "position": {},
+    "filter": {},
     "block": {},
     "embedding": {},
     "head": {},

@@ -7,7 +7,7 @@ inside the next norm kernel.
 """
 from __future__ import annotations
 
-from .base import Block, register_part
+from .base import Block, CacheNeed, register_part
 
 
 @register_part("block", "pre_norm")
@@ -29,5 +29,38 @@ class PreNormBlock(Block):
         h = self.mixer_norm.forward(x, pending, ctx)
         a = self.mixer.forward(h, ctx, cache)
         h = self.feed_forward_norm.forward(x, a, ctx)
+        f = self.feed_forward.forward(h, ctx)
+        return x, f
+
+
+@register_part("block", "pre_norm_filtered")
+class PreNormFilteredBlock(Block):
+    """The pre-norm arrangement with a filter over time between each norm and its sub-layer:
+    x = x + mixer(filter1(norm1(x))); x = x + ffn(filter2(norm2(x))). Either filter, and the whole feed-forward half,
+    may be left out. The filters' states belong to the layer's cache, beside the mixer's, under "mixer_filter.*" and
+    "feed_forward_filter.*"."""
+
+    wants = {"mixer_norm": "norm", "mixer_filter": "filter", "mixer": "mixer", "feed_forward_norm": "norm",
+             "feed_forward_filter": "filter", "feed_forward": "feed_forward"}
+    optional = ("mixer_filter", "feed_forward_norm", "feed_forward_filter", "feed_forward")
+
+    def cache_need(self):
+        needs = [("", self.mixer.cache_need())]
+        for name in ("mixer_filter", "feed_forward_filter"):
+            part = getattr(self, name)
+            if part is not None:
+                needs.append((name + ".", part.cache_need()))
+        return CacheNeed.merged(needs)
+
+    def forward(self, x, pending, ctx, cache):
+        h = self.mixer_norm.forward(x, pending, ctx)
+        if self.mixer_filter is not None:
+            h = self.mixer_filter.forward(h, ctx, cache, prefix="mixer_filter.")
+        a = self.mixer.forward(h, ctx, cache)
+        if self.feed_forward is None:
+            return x, a
+        h = self.feed_forward_norm.forward(x, a, ctx)
+        if self.feed_forward_filter is not None:
+            h = self.feed_forward_filter.forward(h, ctx, cache, prefix="feed_forward_filter.")
         f = self.feed_forward.forward(h, ctx)
         return x, f

@@ -1,0 +1,62 @@
+"""A feed-forward of routed experts: each token goes through the ``top`` best of ``experts`` small gated feed-forwards.
+
+Router logits z = W_router h are float; scores are sigmoid(z) (or a softmax over the experts); the ``top`` largest
+are chosen, lowest index first on ties; the weights are the chosen scores, divided by their sum only if asked. The
+weight multiplies the expert's input (``scale_input``), which matters because the experts are not linear, or its
+output. Expert activations: "clamped_swish": g = min(gate, limit), u = clamp(up, -limit, limit), g * sigmoid(alpha g)
+* (u + 1); "swiglu": silu(gate) * up. The experts' matrices are stacked at load into [E, 2 ff, hidden] (gate rows,
+then up rows) and [E, hidden, ff]; tokens are grouped by expert on the device, so a step has no host round trip
+(csrc/routed_experts.cu).
+"""
+from __future__ import annotations
+
+import torch
+
+from .base import FeedForward, TensorDecl, register_part
+
+
+@register_part("feed_forward", "routed_experts")
+class RoutedExperts(FeedForward):
+    """params: hidden, experts, top, ff, score ("sigmoid" | "softmax"), renormalise, scale_input, activation, limit, alpha,
+    names: router, and expert tensor names as patterns with {e} (defaults "router", "e{e}.gate", "e{e}.up", "e{e}.down")."""
+
+    def __init__(self, spec, runtime):
+        super().__init__(spec, runtime)
+        p = spec.params
+        self.hidden, self.experts, self.top, self.ff = int(p["hidden"]), int(p["experts"]), int(p["top"]), int(p["ff"])
+        if not (1 <= self.top <= self.experts) or self.top > 16:
+            raise ValueError(f"top {self.top} of {self.experts} experts is not possible (at most 16 per token)")
+        self.score = p.get("score", "sigmoid")
+        self.renormalise = bool(p.get("renormalise", False))
+        self.scale_input = bool(p.get("scale_input", True))
+        self.activation = p.get("activation", "clamped_swish")
+        self.limit = float(p.get("limit", 0.0))
+        self.alpha = float(p.get("alpha", 1.702))
+        names = dict(p.get("names", {}))
+        self.router_name = self.prefix + names.get("router", "router")
+        self.patterns = {k: self.prefix + names.get(k, "e{e}." + k) for k in ("gate", "up", "down")}
+        self.w_router = self.w_gate_up = self.w_down = None
+
+    def tensor_decls(self):
+        decls = [TensorDecl(self.router_name, (self.experts, self.hidden))]
+        for e in range(self.experts):
+            decls += [TensorDecl(self.patterns["gate"].format(e=e), (self.ff, self.hidden)),
+                      TensorDecl(self.patterns["up"].format(e=e), (self.ff, self.hidden)),
+                      TensorDecl(self.patterns["down"].format(e=e), (self.hidden, self.ff))]
+        return decls
+
+    def load(self, tensors):
+        self.w_router = tensors[self.router_name].contiguous()
+        self.w_gate_up = torch.stack([torch.cat([tensors[self.patterns["gate"].format(e=e)], tensors[self.patterns["up"].format(e=e)]], 0)
+                                      for e in range(self.experts)]).contiguous()
+        self.w_down = torch.stack([tensors[self.patterns["down"].format(e=e)] for e in range(self.experts)]).contiguous()
+
+    def forward(self, h, ctx):
+        rt = self.rt
+        t = h.shape[0]
+        logits = torch.empty((t, self.experts), dtype=torch.float32, device=rt.device)
+        rt.kernels.linear(h, self.w_router, logits)
+        out = rt.empty_act((t, self.hidden))
+        rt.kernels.routed_experts(h, logits, self.w_gate_up, self.w_down, self.top, out, score=self.score, renormalise=self.renormalise,
+                                  scale_input=self.scale_input, activation=self.activation, limit=self.limit, alpha=self.alpha)
+        return out

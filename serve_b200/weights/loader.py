@@ -77,7 +77,8 @@ def load_weights(model, model_dir: str, compute_dtype: torch.dtype, device) -> N
     for n, d in decls.items():
         if n in where:
             _, shape = where[n].info(n)
-            if tuple(shape) != tuple(d.shape):
+            # a declared size of -1 stands for "whatever the file has" (the part checks what it finds at load)
+            if len(shape) != len(d.shape) or any(want != -1 and want != have for want, have in zip(d.shape, shape)):
                 wrong.append(f"{n}: file has {list(shape)}, model wants {list(d.shape)}")
     if missing or unexpected or wrong:
         lines = [f"weights in {model_dir!r} do not fit the model:"]

@@ -101,7 +101,7 @@ class EmuKernels:
             v_cache[pages, :, pos % page_size] = x[:, heads + kv_heads:]
 
     def attention(self, qkv, k_cache, v_cache, block_table, cu_q, kv_len, token_row, positions, heads, kv_heads, head_dim,
-                  page_size, scale, window, out, shape):
+                  page_size, scale, window, out, shape, slopes=None, chunk=0):
         d = head_dim
         g = heads // kv_heads
         cu = cu_q.tolist()
@@ -114,6 +114,8 @@ class EmuKernels:
             q = qkv[q0:q1, : heads * d].view(n, heads, d).to(self.math)
             key_pos = torch.arange(L, device=qkv.device)
             lo = max(0, (L - n) - window + 1) if window else 0
+            if chunk:
+                lo = max(lo, ((L - n) // chunk) * chunk)
             pages = block_table[r].long()[key_pos[lo:] // page_size]
             assert bool((pages >= 0).all()), "attention reads a missing page"
             k = k_cache[pages, :, key_pos[lo:] % page_size].to(self.math)
@@ -125,9 +127,135 @@ class EmuKernels:
             mask = kp > qp
             if window:
                 mask = mask | (kp <= qp - window)
+            if chunk:
+                mask = mask | (kp < (qp // chunk) * chunk)
+            if slopes is not None:
+                s = s - slopes.to(self.math)[:, None, None] * (qp - kp).to(self.math)[None]
             s = s.masked_fill(mask[None], float("-inf"))
             o = torch.einsum("hts,shd->thd", torch.softmax(s, -1), vv)
             out[q0:q1] = o.reshape(n, heads * d).to(out.dtype)
+
+    # ---- mixers with recurrent state, routed experts -------------------------------------------------------------
+    def causal_conv(self, x, weight, bias, state, ctx, out, activation="none", residual=False):
+        taps = weight.shape[1]
+        k = taps - 1
+        cu = ctx.cu_q.tolist()
+        w = weight.to(self.math)
+        for r, slot in enumerate(ctx.slots.tolist()):
+            a, b = cu[r], cu[r + 1]
+            seq = torch.cat([state[slot].to(self.math), x[a:b].to(self.math)], 0)          # [k + n, C]
+            acc = torch.zeros((b - a, x.shape[1]), dtype=self.math, device=x.device)
+            for j in range(taps):
+                acc = acc + seq[j: j + b - a] * w[:, j]
+            if bias is not None:
+                acc = acc + bias.to(self.math)
+            if residual:
+                acc = acc + x[a:b].to(self.math)
+            if activation == "silu":
+                acc = acc * torch.sigmoid(acc)
+            out[a:b] = acc.to(out.dtype)
+            if k:
+                state[slot] = seq[-k:].to(state.dtype)
+
+    def linear_recurrence(self, mode, q, k, v, state, ctx, out, heads, qk_heads, dk, dv, aux=None, rate=None, decay=None,
+                          a_log=None, dt_bias=None, d_skip=None, q_scale=1.0):
+        m = self.math
+        f = torch.nn.functional
+        cu = ctx.cu_q.tolist()
+        rep = heads // qk_heads
+        for r, slot in enumerate(ctx.slots.tolist()):
+            a, b = cu[r], cu[r + 1]
+            n = b - a
+            qq = q[a:b, : qk_heads * dk].to(m).reshape(n, qk_heads, dk).repeat_interleave(rep, 1)
+            kk = k[a:b, : qk_heads * dk].to(m).reshape(n, qk_heads, dk).repeat_interleave(rep, 1)
+            vv = v[a:b, : heads * dv].to(m).reshape(n, heads, dv)
+            s = state[slot].to(m)                                                            # [heads, dk, dv]
+            if mode == "decay":
+                qq, kk, vv = f.silu(qq), f.silu(kk), f.silu(vv)
+                dec = decay.to(m)[None, :, None].expand(n, heads, dk)
+                u_scale = torch.ones(n, heads, dtype=m, device=q.device)
+            elif mode == "ssm":
+                dt = f.softplus(aux[a:b, :heads].to(m) + dt_bias.to(m), threshold=20.0)
+                dec = torch.exp(-torch.exp(a_log.to(m)) * dt)[:, :, None].expand(n, heads, dk)
+                u_scale = dt
+            else:
+                qq = qq / torch.sqrt((qq * qq).sum(-1, keepdim=True) + 1e-6) * q_scale
+                kk = kk / torch.sqrt((kk * kk).sum(-1, keepdim=True) + 1e-6)
+                rr = f.softplus(rate[a:b, : heads * dk].to(m) + dt_bias.to(m), threshold=20.0).reshape(n, heads, dk)
+                dec = torch.exp(-torch.exp(a_log.to(m))[None, :, None] * rr)
+                beta = torch.sigmoid(aux[a:b, :heads].to(m))
+            for i in range(n):
+                s = s * dec[i][:, :, None]
+                if mode == "delta":
+                    u = beta[i][:, None] * (vv[i] - torch.einsum("hkv,hk->hv", s, kk[i]))
+                else:
+                    u = u_scale[i][:, None] * vv[i]
+                s = s + kk[i][:, :, None] * u[:, None, :]
+                o = torch.einsum("hkv,hk->hv", s, qq[i])
+                if mode == "ssm":
+                    o = o + d_skip.to(m)[:, None] * vv[i]
+                out[a + i] = o.reshape(-1).to(out.dtype)
+            state[slot] = s.to(state.dtype)
+
+    def gated_norm(self, y, out, groups=0, eps=0.0, weight=None, gate=None, gate_act="sigmoid", gate_first=False, scale=1.0):
+        m = self.math
+        v = y.to(m)
+        t, c = v.shape
+        g = None
+        if gate is not None:
+            g = gate.to(m)
+            g = g * torch.sigmoid(g) if gate_act == "silu" else torch.sigmoid(g)
+            g = g.repeat_interleave(c // gate.shape[1], 1)
+        if g is not None and gate_first:
+            v = v * g
+        if groups:
+            v = v.reshape(t, groups, c // groups)
+            v = (v / torch.sqrt((v * v).mean(-1, keepdim=True) + eps)).reshape(t, c)
+        if weight is not None:
+            v = v * weight.to(m).repeat(c // weight.shape[0])
+        if g is not None and not gate_first:
+            v = v * g
+        out.copy_((v * scale).to(out.dtype))
+
+    def kv_norm_cache_write(self, qkv, positions, token_row, heads, kv_heads, head_dim, norm_dim, eps, k_cache, v_cache, block_table,
+                            page_size):
+        t, d = qkv.shape[0], head_dim
+        x = qkv[:, : (heads + 2 * kv_heads) * d].reshape(t, heads + 2 * kv_heads, d)
+        kk, vv = x[:, heads: heads + kv_heads], x[:, heads + kv_heads:].to(self.math)
+        if norm_dim:
+            vv = vv / torch.sqrt((vv[..., :norm_dim] ** 2).mean(-1, keepdim=True) + eps)
+        pos = positions.long()
+        pages = block_table.long()[token_row.long(), pos // page_size]
+        assert bool((pages >= 0).all()), "cache write to a missing page"
+        k_cache[pages, :, pos % page_size] = kk
+        v_cache[pages, :, pos % page_size] = vv.to(v_cache.dtype)
+
+    def routed_experts(self, h, logits, w_gate_up, w_down, top, out, score="sigmoid", renormalise=False, scale_input=True,
+                       activation="clamped_swish", limit=0.0, alpha=1.702):
+        m = self.math
+        z = logits.to(torch.float32)
+        scores = torch.sigmoid(z) if score == "sigmoid" else torch.softmax(z, -1)
+        wts, idx = torch.topk(scores, top, dim=-1)
+        if renormalise:
+            wts = wts / wts.sum(-1, keepdim=True)
+        ff = w_down.shape[2]
+        total = torch.zeros((h.shape[0], w_down.shape[1]), dtype=m, device=h.device)
+        for slot in range(top):
+            for e in idx[:, slot].unique().tolist():
+                rows = (idx[:, slot] == e).nonzero().flatten()
+                w = wts[rows, slot].to(m)[:, None]
+                gu = h[rows].to(m) @ w_gate_up[e].to(m).T
+                if scale_input:
+                    gu = gu * w
+                g, u = gu[:, :ff], gu[:, ff:]
+                if activation == "clamped_swish":
+                    g, u = torch.clamp(g, max=limit), torch.clamp(u, -limit, limit)
+                    a = g * torch.sigmoid(alpha * g) * (u + 1)
+                else:
+                    a = g * torch.sigmoid(g) * u
+                y = a.to(h.dtype).to(m) @ w_down[e].to(m).T
+                total[rows] += y if scale_input else y * w
+        out.copy_(total.to(out.dtype))
 
     def sample(self, logits, temperature, req_ids, tok_index, seed, out, slots=None, last_token=None):
         from tests.plain.llama_plain import sample_token
