@@ -143,7 +143,7 @@ class EmuKernels:
         w = weight.to(self.math)
         for r, slot in enumerate(ctx.slots.tolist()):
             a, b = cu[r], cu[r + 1]
-            seq = torch.cat([state[slot].to(self.math), x[a:b].to(self.math)], 0)          # [k + n, C]
+            seq = x[a:b].to(self.math) if not k else torch.cat([state[slot].to(self.math), x[a:b].to(self.math)], 0)   # [k + n, C]
             acc = torch.zeros((b - a, x.shape[1]), dtype=self.math, device=x.device)
             for j in range(taps):
                 acc = acc + seq[j: j + b - a] * w[:, j]

@@ -152,11 +152,16 @@ def expert(x, w, p, limit):
     return (g * torch.sigmoid(1.702 * g) * (u + 1)) @ w[p + "down"].T
 
 
-def routed_experts(h, w, p, f):
-    """Sigmoid router; each token's input is scaled by the score of each of its `top` experts."""
+def routed_experts(h, w, p, f, margins: list = None):
+    """Sigmoid router; each token's input is scaled by the score of each of its `top` experts. ``margins``, if a list,
+    receives the smallest gap between a chosen and a rejected expert's logit (how close the closest call was)."""
     n, top, limit = f["router"]["experts"], f["router"]["top"], f["expert"]["limit"]
-    scores = torch.sigmoid(h @ w[p + "router"].T)
+    z = h @ w[p + "router"].T
+    scores = torch.sigmoid(z)
     best = torch.topk(scores, top, dim=-1).indices
+    if margins is not None and top < n:
+        ranked = torch.sort(z, dim=-1, descending=True).values
+        margins.append(float((ranked[:, top - 1] - ranked[:, top]).min()))
     out = torch.zeros_like(h)
     for e in range(n):
         for slot in range(top):
@@ -167,8 +172,9 @@ def routed_experts(h, w, p, f):
 
 
 # ---- the model ----------------------------------------------------------------------------------------------
-def forward(w: Dict[str, torch.Tensor], cfg: dict, tokens: List[int], residuals: list = None):
-    """Logits [T, vocab] of one sequence; ``residuals``, if a list, receives the stream after every layer."""
+def forward(w: Dict[str, torch.Tensor], cfg: dict, tokens: List[int], residuals: list = None, margins: list = None):
+    """Logits [T, vocab] of one sequence; ``residuals``, if a list, receives the stream after every layer, and
+    ``margins`` the closest call of every router."""
     eps = cfg["norm"]["eps"]
     x = w["embed"][torch.as_tensor(tokens, dtype=torch.long)]
     for i, layer in enumerate(cfg["layers"]):
@@ -177,7 +183,7 @@ def forward(w: Dict[str, torch.Tensor], cfg: dict, tokens: List[int], residuals:
         x = x + MIXERS[layer["type"]](h, w, p + "mix.", layer["mixer"], eps)
         if layer.get("mlp") is not None:
             h = input_conv(rms_norm(x, w[p + "norm2"], eps), w[p + "canon2"])
-            x = x + routed_experts(h, w, p + "mlp.", layer["mlp"])
+            x = x + routed_experts(h, w, p + "mlp.", layer["mlp"], margins)
         if residuals is not None:
             residuals.append(x.clone())
     return rms_norm(x, w["final.norm"], eps) @ w["embed"].T

@@ -1,0 +1,135 @@
+"""Shared by the Rogisun tests: small configurations of their own, seeded weights, engines on either backend.
+
+Two backends: "emu" runs the engine's own parts, cache and step function on the CPU over the torch stand-ins of
+tests/emu_kernels.py (no GPU needed, float32); "cuda" runs the real kernels. The oracle is tests/plain/rogisun_plain.py
+in float64.
+"""
+from __future__ import annotations
+
+import copy
+import json
+import os
+
+import pytest
+import torch
+
+from tests.plain import rogisun_plain as P
+
+MOE = lambda experts, top, ff, limit: {"kind": "moe", "expert": {"ff": ff, "limit": limit}, "router": {"experts": experts, "top": top}}
+
+# Sizes differ between layers and from each other wherever the design allows: two experts per token and one; groups
+# of heads that share keys on either side of the parallel pair; query/key size below and above the value size (the
+# second needs padding to a head size of 32); blocks of positions that are no multiple of a cache page; a layer
+# without a feed-forward; convolutions of 2, 3 and 4 taps.
+CONFIGS = {
+    "p": {"architecture": "Rogisun", "width": 64, "vocab": 160, "norm": {"eps": 1e-5}, "canon": {"taps": 3}, "layers": [
+        {"type": "lightning", "mixer": {"heads": 2, "dim": 16, "vdim": 24, "decay": [0.9, 0.985]}, "mlp": MOE(4, 2, 24, 1.5)},
+        {"type": "parallel", "mixer": {
+            "left": {"heads": 4, "kv_heads": 2, "dim": 16, "vdim": 32, "scale": 0.3, "mask": {"size": 24}},
+            "right": {"heads": 4, "kv_heads": 2, "dim": 16, "vdim": 8, "conv": 2, "rank": 8},
+            "left_scale": 0.7, "right_scale": 1.3}, "mlp": None},
+        {"type": "mamba2", "mixer": {"heads": 4, "vdim": 8, "state": 12, "groups": 2, "norm_groups": 2, "conv": 3}, "mlp": MOE(3, 1, 16, 0.8)},
+    ]},
+    "q": {"architecture": "Rogisun", "width": 48, "vocab": 97, "norm": {"eps": 1e-6}, "canon": {"taps": 2}, "layers": [
+        {"type": "parallel", "mixer": {
+            "left": {"heads": 3, "kv_heads": 3, "dim": 24, "vdim": 16, "scale": 0.25, "mask": {"size": 10}},
+            "right": {"heads": 2, "kv_heads": 1, "dim": 24, "vdim": 16, "conv": 4, "rank": 6},
+            "left_scale": 1.0, "right_scale": 0.5}, "mlp": MOE(5, 3, 8, 2.0)},
+        {"type": "mamba2", "mixer": {"heads": 2, "vdim": 16, "state": 20, "groups": 1, "norm_groups": 1, "conv": 2}, "mlp": None},
+        {"type": "lightning", "mixer": {"heads": 3, "dim": 8, "vdim": 16, "decay": [0.5, 0.93, 0.999]}, "mlp": MOE(2, 1, 32, 1.0)},
+    ]},
+}
+
+
+def make_weights(cfg: dict, seed: int, router_gain: float = 6.0):
+    """float32 weights by name, sized so that every layer's output matters; routers with a wide spread of logits."""
+    g = torch.Generator().manual_seed(seed)
+    w = {}
+    for name, shape in P.tensor_shapes(cfg).items():
+        leaf = name.split(".")[-1]
+        if name.endswith(("canon1", "canon2", ".conv")):
+            t = torch.randn(shape, generator=g) * 0.4
+        elif leaf in ("norm", "norm1", "norm2", "D"):
+            t = 1.0 + 0.2 * torch.randn(shape, generator=g)
+        elif leaf == "A_log":
+            t = torch.rand(shape, generator=g) * 1.5 - 1.0
+        elif leaf in ("dt_bias", "b"):
+            t = torch.randn(shape, generator=g) * 0.5
+        elif leaf == "embed":
+            t = torch.randn(shape, generator=g)
+        elif leaf == "router":
+            t = torch.randn(shape, generator=g) * router_gain / shape[-1] ** 0.5
+        else:
+            t = torch.randn(shape, generator=g) * 1.5 / shape[-1] ** 0.5
+        w[name] = t.bfloat16().float()          # values that a bfloat16 file holds exactly
+    return w
+
+
+def plain_logits(w, cfg, tokens, margins=None):
+    w64 = {k: v.double() for k, v in w.items()}
+    with torch.no_grad():
+        return P.forward(w64, cfg, tokens, margins=margins).float()
+
+
+def settled_weights(cfg: dict, requests, min_margin: float = 0.05):
+    """Weights (by trying seeds) with which no router decision on the given requests is a close call: a test in
+    bfloat16 must not hinge on which of two nearly equal experts wins."""
+    for seed in range(100, 140):
+        w = make_weights(cfg, seed)
+        margins = []
+        plain = {rid: plain_logits(w, cfg, toks, margins) for rid, toks in requests.items()}
+        if not margins or min(margins) >= min_margin:
+            return w, plain
+    raise AssertionError("no seed gives clear router decisions; widen the routers' spread")
+
+
+def write_model(path: str, cfg: dict, w, dtype=torch.float32) -> str:
+    from safetensors.torch import save_file
+
+    os.makedirs(path, exist_ok=True)
+    with open(os.path.join(path, "config.json"), "w") as f:
+        json.dump(cfg, f)
+    save_file({k: v.to(dtype).contiguous() for k, v in w.items()}, os.path.join(path, "model.safetensors"))
+    return path
+
+
+BACKENDS = [pytest.param(("emu", "float32"), id="emu"),
+            pytest.param(("cuda", "float32"), id="cuda-f32", marks=pytest.mark.gpu),
+            pytest.param(("cuda", "bfloat16"), id="cuda-bf16", marks=pytest.mark.gpu)]
+
+
+def runtime_for(backend):
+    """(Runtime, device) of a backend, for tests that build single parts."""
+    from serve_b200.engine.runtime import Runtime
+
+    kind, dtype = backend
+    dt = {"float32": torch.float32, "bfloat16": torch.bfloat16}[dtype]
+    if kind == "emu":
+        from tests.emu_kernels import EmuKernels
+
+        return Runtime(EmuKernels("cpu", torch.float64), "cpu", dt), "cpu"
+    from serve_b200.kernels import load_kernels
+
+    return Runtime(load_kernels("cuda:0"), "cuda:0", dt), "cuda:0"
+
+
+def make_engine(folder, backend, page, num_pages, max_slots=4, graphs=False, budget=512, context=None):
+    from serve_b200.config import EngineConfig
+    from serve_b200.engine import Engine
+
+    kind, dtype = backend
+    ec = EngineConfig(dtype=dtype, page_size=page, num_pages=num_pages, max_slots=max_slots, max_tokens_per_step=budget,
+                      max_context=context or num_pages * page, use_cuda_graphs=graphs and kind == "cuda",
+                      device="cpu" if kind == "emu" else "cuda:0")
+    if kind == "emu":
+        from tests.emu_kernels import EmuKernels
+
+        return Engine.from_folder(folder, ec, kernels=EmuKernels("cpu"))
+    return Engine.from_folder(folder, ec)
+
+
+def tolerance(backend, plain) -> float:
+    """float32: rounding of float sums. bfloat16: activations are rounded to 8 bits several times a layer; the bound is
+    2^-5 of the largest logit (these models have convolutions and recurrences between the roundings)."""
+    scale = max(float(p.abs().max()) for p in plain.values())
+    return scale * (2e-4 if backend[1] == "float32" else 2.0 ** -5)

@@ -1,0 +1,398 @@
+"""The Rogisun decoder in the engine against the plain implementation of tests/plain/rogisun_plain.py.
+
+Every test runs on the CPU over the torch stand-ins of the kernels (which checks the parts, the cache and state
+manager, the step function and the scheduler) and, marked gpu, on the real kernels in float32 and bfloat16.
+"""
+import math
+
+import pytest
+import torch
+
+from serve_b200.cache import CacheManager
+from serve_b200.config import ConfigError, PartSpec, build_spec, config_from_dict
+from serve_b200.engine.step import BatchShape, StepContext
+from serve_b200.parts import build_part
+from tests import helpers
+from tests.plain import rogisun_plain as P
+from tests.rogisun_cases import BACKENDS, CONFIGS, make_engine, make_weights, plain_logits, runtime_for, settled_weights, tolerance, write_model
+
+LENGTHS = {"p": [1, 5, 23, 49, 75, 130], "q": [2, 9, 31, 64, 101]}
+PAGE = {"p": 8, "q": 16}
+
+
+# ---- configuration and description ----------------------------------------------------------------------------
+def test_configuration_is_read_from_the_file_and_describes_every_layer():
+    from serve_b200.weights.random_init import model_tensor_decls
+
+    for name, raw in CONFIGS.items():
+        cfg = config_from_dict(raw)
+        assert type(cfg).__name__ == "RogisunConfig" and cfg.width == raw["width"] and cfg.canon_taps == raw["canon"]["taps"]
+        spec = build_spec(cfg)
+        assert [l.parts["mixer"].kind for l in spec.layers] == [l["type"] for l in raw["layers"]]
+        assert [("feed_forward" in l.parts) for l in spec.layers] == [l["mlp"] is not None for l in raw["layers"]]
+        decls = {n: tuple(d.shape) for n, d in model_tensor_decls(cfg).items()}
+        assert decls == P.tensor_shapes(raw)
+        assert config_from_dict(cfg.to_dict()) == cfg
+
+
+@pytest.mark.parametrize("breaker", [
+    lambda c: c["layers"][0].update(type="other"),
+    lambda c: c["layers"][0]["mixer"].pop("heads"),
+    lambda c: c.pop("canon"),
+    lambda c: c["layers"][0]["mlp"]["router"].update(top=99),
+    lambda c: c["layers"][1]["mixer"]["left"].update(kv_heads=3),
+])
+def test_configuration_refuses_what_it_cannot_run(breaker):
+    import copy
+
+    raw = copy.deepcopy(CONFIGS["p"])
+    breaker(raw)
+    with pytest.raises(ConfigError):
+        config_from_dict(raw)
+
+
+def test_a_file_decides_the_width_of_the_two_step_projections(tmp_path):
+    """Without a rank in the configuration the delta-rule mixer takes it from the shapes in the file."""
+    import copy
+
+    raw = copy.deepcopy(CONFIGS["q"])
+    w = make_weights(raw, 3)
+    folder = write_model(str(tmp_path / "m"), raw, w)
+    del raw["layers"][0]["mixer"]["right"]["rank"]
+    import json, os
+
+    with open(os.path.join(folder, "config.json"), "w") as f:
+        json.dump(raw, f)
+    eng = make_engine(folder, ("emu", "float32"), 16, 8)
+    toks = helpers.random_tokens(raw["vocab"], 12, 1)
+    got = helpers.replay(eng, helpers.trace_whole({"a": toks}))
+    helpers.compare_with_plain(got, {"a": plain_logits(w, CONFIGS["q"], toks)}, atol=2e-4)
+
+
+# ---- whole models under every way of cutting the work ------------------------------------------------------------
+@pytest.fixture(scope="module")
+def models(tmp_path_factory):
+    out = {}
+    for name, cfg in CONFIGS.items():
+        reqs = {f"r{i}": helpers.random_tokens(cfg["vocab"], n, seed=20 + i) for i, n in enumerate(LENGTHS[name])}
+        w, plain = settled_weights(cfg, reqs)
+        out[name] = (w, reqs, plain, {dt: write_model(str(tmp_path_factory.mktemp(f"{name}-{dt}")), cfg, w, getattr(torch, dt))
+                                      for dt in ("float32", "bfloat16")})
+    return out
+
+
+@pytest.mark.parametrize("backend", BACKENDS)
+@pytest.mark.parametrize("name", ["p", "q"])
+@pytest.mark.parametrize("cut", ["whole", "tail_decode", "portions", "single_tokens"])
+def test_cuts_match_plain(models, name, backend, cut):
+    w, reqs, plain, folders = models[name]
+    page = PAGE[name]
+    eng = make_engine(folders[backend[1]], backend, page, num_pages=-(-160 // page) * 2, graphs=(cut == "tail_decode"))
+    if cut == "single_tokens":
+        steps = helpers.trace_tail_decode({k: v for k, v in reqs.items() if len(v) <= 50}, tail=10 ** 6)
+    else:
+        make = {"whole": helpers.trace_whole, "tail_decode": lambda r: helpers.trace_tail_decode(r, tail=40),
+                "portions": lambda r: helpers.trace_portions(r, sizes=(7, 2, 19, 1, 3, 2, 33, 5, 2, 11))}[cut]
+        steps = make(reqs)
+    with torch.inference_mode():
+        got = helpers.replay(eng, steps)
+    eng.kernels.check_errors()
+    helpers.compare_with_plain(got, plain, atol=tolerance(backend, plain))
+    eng.cache.check()
+    assert eng.cache.live == 0
+
+
+@pytest.mark.parametrize("backend", BACKENDS)
+@pytest.mark.parametrize("name", ["p", "q"])
+def test_mixed_batches_with_pages_and_slots_used_again(models, name, backend):
+    """Unequal requests side by side, portions beside single tokens, fewer slots and pages than requests: every
+    row must equal the request run alone. Pages and states are poisoned first, so that a page or a state that is
+    read without having been written (or cleared) shows."""
+    w, reqs, plain, folders = models[name]
+    page = PAGE[name]
+    steps = helpers.trace_mixed(reqs, live=3, seed=7)
+    need = helpers.tokens_needed(steps, page) // page
+    assert need < sum(-(-len(t) // page) for t in reqs.values())
+    # behind the start of a query's block of positions no key is read again: the cache manager gives those pages back at
+    # once, so three live requests get by with what a block and a portion span, far fewer pages than their tokens
+    block = next(l["mixer"]["left"]["mask"]["size"] for l in CONFIGS[name]["layers"] if l["type"] == "parallel")
+    pool = min(need, 3 * CacheManager.most_pages_of_a_request(None, page, 160, 21, block))
+    assert pool < sum(-(-len(t) // page) for t in reqs.values())
+    eng = make_engine(folders[backend[1]], backend, page, num_pages=pool, max_slots=3, context=160)
+    for view in eng.stepper.views:
+        if view.k is not None:
+            view.k.fill_(float("nan"))
+            view.v.fill_(float("nan"))
+        for st in view.states.values():
+            st.fill_(float("nan"))
+    with torch.inference_mode():
+        got = helpers.replay(eng, steps)
+    eng.kernels.check_errors()
+    helpers.compare_with_plain(got, plain, atol=tolerance(backend, plain))
+    eng.cache.check()
+    assert eng.cache.live == 0 and eng.cache.free_slots == 3
+    assert max(g.pool.high_water for g in eng.cache.groups) <= pool
+
+
+@pytest.mark.parametrize("backend", BACKENDS)
+def test_long_decoding_side_by_side(models, backend):
+    """Two requests decoded one token at a time for 120 steps after short prompts (from CUDA graphs on the GPU): the
+    states are carried through every step, and the blocks of positions and the pages are crossed many times."""
+    cfg = CONFIGS["q"]
+    w = models["q"][0]
+    seqs = {f"d{i}": helpers.random_tokens(cfg["vocab"], 140 - 9 * i, seed=60 + i) for i in range(2)}
+    plain = {rid: plain_logits(w, cfg, toks) for rid, toks in seqs.items()}
+    eng = make_engine(models["q"][3][backend[1]], backend, 16, num_pages=24, graphs=True)
+    steps = [{"step": 0, "entries": [{"id": rid, "tokens": t[:11 + 6 * i], "want": [10 + 6 * i]} for i, (rid, t) in enumerate(seqs.items())], "end": []}]
+    at = {rid: 11 + 6 * i for i, rid in enumerate(seqs)}
+    while any(at[rid] < len(seqs[rid]) for rid in seqs):
+        entries = [{"id": rid, "tokens": [t[at[rid]]], "want": [0]} for rid, t in seqs.items() if at[rid] < len(t)]
+        for e in entries:
+            at[e["id"]] += 1
+        steps.append({"step": len(steps), "entries": entries, "end": []})
+    with torch.inference_mode():
+        got = helpers.replay(eng, steps)
+    eng.kernels.check_errors()
+    if backend[0] == "cuda":
+        assert eng.stepper.launched_graphs > 80
+    helpers.compare_with_plain(got, plain, atol=tolerance(backend, plain))
+
+
+@pytest.mark.parametrize("backend", BACKENDS)
+def test_greedy_generation_through_the_scheduler(models, backend):
+    """generate(): the engine's own entry point, scheduler and sampler. Every generated token must be (within the
+    tolerance) the best one of the plain model given the tokens before it."""
+    from serve_b200.run import Request, generate
+
+    cfg = CONFIGS["p"]
+    w, reqs, _, folders = models["p"]
+    eng = make_engine(folders[backend[1]], backend, 8, num_pages=40, max_slots=3, budget=32)
+    prompts = [reqs["r1"], reqs["r2"], reqs["r3"][:30], reqs["r0"]]
+    out = generate(eng, [Request(torch.tensor(p), len(p), 12) for p in prompts], temperature=0.0, eos_token_id=None)
+    for p, r in zip(prompts, out):
+        new = r.generated_tokens.tolist()
+        assert len(new) == 12
+        logits = plain_logits(w, cfg, p + new)
+        tol = float(logits.abs().max()) * (2e-4 if backend[1] == "float32" else 2.0 ** -5)
+        for i, tok in enumerate(new):
+            row = logits[len(p) - 1 + i]
+            assert float(row[tok]) >= float(row.max()) - 2 * tol, f"token {i} of a request is not the plain model's choice"
+    assert eng.cache.live == 0
+
+
+# ---- each mechanism alone ---------------------------------------------------------------------------------------
+def _ctx(rt, dev, q_lens, starts, slots, mgr=None, rids=None):
+    t = sum(q_lens)
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=dev)
+    pos = [s + j for q, s in zip(q_lens, starts) for j in range(q)]
+    row = [i for i, q in enumerate(q_lens) for _ in range(q)]
+    cu = [0]
+    for q in q_lens:
+        cu.append(cu[-1] + q)
+    kv = [s + q for q, s in zip(q_lens, starts)]
+    tables = [torch.from_numpy(mgr.table_rows(g, rids)).to(dev) for g in range(len(mgr.groups))] if mgr is not None else []
+    return StepContext(rt=rt, shape=BatchShape(len(q_lens), t, max(q_lens), min(q_lens), max(kv), all(q == 1 for q in q_lens)),
+                       tokens=i32([0] * t), positions=i32(pos), token_row=i32(row), cu_q=i32(cu), kv_len=i32(kv), slots=i32(slots),
+                       logit_rows=i32([]), block_tables=tables, rids=rids or [])
+
+
+def _run_part(backend, family, spec, weights, x, cuts, page=8):
+    """One part alone over one sequence cut as ``cuts`` says, with a cache manager made for its need; a second request
+    runs first in the same slot and is closed, so the slot's state and pages have been used before."""
+    rt, dev = runtime_for(backend)
+    part = build_part(family, spec, rt)
+    names = {d.name for d in part.tensor_decls()}
+    part.load({n: weights[n].to(dev).to(rt.act_dtype) for n in names})
+    need = part.cache_need() if hasattr(part, "cache_need") else None
+    mgr = CacheManager([need], [None], page, 64, 1, 256, device=dev, kv_dtype=rt.act_dtype)
+    view = mgr.views()[0]
+
+    def call(h, ctx):
+        if family == "mixer":
+            return part.forward(h, ctx, view)
+        if family == "filter":
+            return part.forward(h, ctx, view)
+        return part.forward(h, ctx)
+
+    xs = x.to(dev).to(rt.act_dtype)
+    with torch.inference_mode():
+        mgr.open("warm")
+        mgr.reserve([("warm", 5)])
+        call(torch.randn_like(xs[:5]), _ctx(rt, dev, [5], [0], [mgr.slot("warm")], mgr, ["warm"]))
+        mgr.close("warm")
+        mgr.open("r")
+        outs, at = [], 0
+        for n in cuts:
+            mgr.reserve([("r", at + n)])
+            outs.append(call(xs[at: at + n], _ctx(rt, dev, [n], [at], [mgr.slot("r")], mgr, ["r"])).float().cpu())
+            mgr.commit("r", at + n)
+            at += n
+    assert at == x.shape[0]
+    rt.kernels.check_errors()
+    return torch.cat(outs)
+
+
+def _tol(backend, want):
+    return float(want.abs().max()) * (1e-4 if backend[1] == "float32" else 2.0 ** -6)
+
+
+def _layer(name, index):
+    cfg = CONFIGS[name]
+    return cfg, cfg["layers"][index], f"l{index}."
+
+
+CUTS = [[57], [30, 1, 1, 2, 5, 17, 1], [1] * 57]
+
+
+def _mixer_case(backend, name, index, cuts, seed=5, x=None, tweak=None):
+    from serve_b200.models.rogisun import _mixer_spec
+
+    cfg, layer, p = _layer(name, index)
+    w = make_weights(cfg, seed)
+    if tweak is not None:
+        tweak(w, p + "mix.")
+    g = torch.Generator().manual_seed(seed + 1)
+    if x is None:
+        x = torch.randn(sum(cuts), cfg["width"], generator=g)
+    x = x.bfloat16().float()
+    spec = _mixer_spec(layer["type"], layer["mixer"], cfg["width"], cfg["norm"]["eps"], p + "mix.")
+    got = _run_part(backend, "mixer", spec, w, x, cuts)
+    want = P.MIXERS[layer["type"]](x.double(), {k: v.double() for k, v in w.items()}, p + "mix.", layer["mixer"], cfg["norm"]["eps"]).float()
+    torch.testing.assert_close(got, want, atol=_tol(backend, want), rtol=0)
+
+
+@pytest.mark.parametrize("backend", BACKENDS)
+@pytest.mark.parametrize("cuts", CUTS, ids=["whole", "portions", "tokens"])
+@pytest.mark.parametrize("where", [("p", 0), ("q", 2)], ids=["p", "q"])
+def test_lightning_mixer_alone(backend, cuts, where):
+    _mixer_case(backend, where[0], where[1], cuts)
+
+
+@pytest.mark.parametrize("backend", BACKENDS)
+@pytest.mark.parametrize("cuts", CUTS, ids=["whole", "portions", "tokens"])
+@pytest.mark.parametrize("where", [("p", 2), ("q", 1)], ids=["p", "q"])
+def test_mamba2_mixer_alone(backend, cuts, where):
+    _mixer_case(backend, where[0], where[1], cuts)
+
+
+@pytest.mark.parametrize("backend", BACKENDS)
+@pytest.mark.parametrize("cuts", CUTS, ids=["whole", "portions", "tokens"])
+@pytest.mark.parametrize("where", [("p", 1), ("q", 0)], ids=["p", "q"])
+def test_parallel_mixer_alone(backend, cuts, where):
+    _mixer_case(backend, where[0], where[1], cuts)
+
+
+@pytest.mark.parametrize("backend", BACKENDS)
+@pytest.mark.parametrize("side,kind", [("left", "distance_bias_attention"), ("right", "gated_delta")])
+@pytest.mark.parametrize("cuts", CUTS[:2], ids=["whole", "portions"])
+def test_each_side_of_the_pair_alone(backend, side, kind, cuts):
+    from serve_b200.models.rogisun import _mixer_spec
+
+    cfg, layer, p = _layer("q", 0)
+    w = make_weights(cfg, 9)
+    x = torch.randn(sum(cuts), cfg["width"], generator=torch.Generator().manual_seed(2)).bfloat16().float()
+    pair = _mixer_spec("parallel", layer["mixer"], cfg["width"], cfg["norm"]["eps"], p + "mix.")
+    spec = pair.params[side]
+    assert spec.kind == kind
+    got = _run_part(backend, "mixer", spec, w, x, cuts, page=16)
+    fn = P.chunked_bias_attention if side == "left" else P.gated_delta_mixer
+    want = fn(x.double(), {k: v.double() for k, v in w.items()}, p + f"mix.{side}.", layer["mixer"][side], cfg["norm"]["eps"]).float()
+    torch.testing.assert_close(got, want, atol=_tol(backend, want), rtol=0)
+
+
+@pytest.mark.parametrize("backend", BACKENDS)
+@pytest.mark.parametrize("far_key,query", [(24, 47), (23, 47), (48, 56), (47, 56), (0, 23), (24, 24)])
+@pytest.mark.parametrize("cuts", [[57], [40] + [1] * 17], ids=["prompt", "decoded"])
+def test_attention_sees_its_block_of_positions_and_nothing_before(backend, far_key, query, cuts):
+    """One key is made to stand out for one query (the query projection is minus the key projection and the query token
+    minus three times the key token, so the query points along that key and away from its own): if the key lies in the query's block of 24 positions it takes nearly all the weight, one position
+    before the block's start it must have none. Positions 23|24 and 47|48 are block edges; pages are 8 tokens, so 24 and
+    48 are page borders as well, and 47 -> 24 is the farthest key a query ever reads."""
+    from serve_b200.models.rogisun import _mixer_spec
+
+    cfg, layer, p = _layer("p", 1)
+    left = p + "mix.left."
+
+    def tweak(w, prefix):
+        d, kvh, heads = layer["mixer"]["left"]["dim"], layer["mixer"]["left"]["kv_heads"], layer["mixer"]["left"]["heads"]
+        wk = w[left + "k"].view(kvh, d, -1)
+        w[left + "q"] = -wk.repeat_interleave(heads // kvh, 0).reshape(heads * d, -1).clone()
+        w[left + "g"] = w[left + "g"] * 0                # every gate at one half
+
+    x = torch.randn(57, cfg["width"], generator=torch.Generator().manual_seed(4)) * 0.3
+    x[far_key] = torch.randn(cfg["width"], generator=torch.Generator().manual_seed(5)) * 1.5
+    if query != far_key:
+        x[query] = -3.0 * x[far_key]
+    pair = _mixer_spec("parallel", layer["mixer"], cfg["width"], cfg["norm"]["eps"], p + "mix.")
+    w = make_weights(cfg, 11)
+    tweak(w, None)
+    xb = x.bfloat16().float()
+    got = _run_part(backend, "mixer", pair.params["left"], w, xb, cuts)
+    w64 = {k: v.double() for k, v in w.items()}
+    want = P.chunked_bias_attention(xb.double(), w64, left, layer["mixer"]["left"], cfg["norm"]["eps"]).float()
+    torch.testing.assert_close(got, want, atol=_tol(backend, want), rtol=0)
+    # the test's own premise: with the key visible the query's output differs a lot from the output without it
+    hidden = dict(layer["mixer"]["left"], mask={"size": 10 ** 6})
+    if far_key // 24 != query // 24:
+        other = P.chunked_bias_attention(xb.double(), w64, left, hidden, cfg["norm"]["eps"]).float()
+        assert float((other[query] - want[query]).abs().max()) > 20 * _tol(backend, want)
+
+
+@pytest.mark.parametrize("backend", BACKENDS)
+@pytest.mark.parametrize("name,index", [("p", 0), ("p", 2), ("q", 0), ("q", 2)])
+def test_routed_experts_alone(backend, name, index):
+    from serve_b200.models.rogisun import rogisun_spec
+
+    cfg, layer, p = _layer(name, index)
+    w = make_weights(cfg, 13)
+    spec = rogisun_spec(config_from_dict(cfg)).layers[index].parts["feed_forward"]
+    for seed in range(50):              # inputs on which no router decision is a close call
+        x = torch.randn(70, cfg["width"], generator=torch.Generator().manual_seed(seed)).bfloat16().float()
+        margins = []
+        want = P.routed_experts(x.double(), {k: v.double() for k, v in w.items()}, p + "mlp.", layer["mlp"], margins).float()
+        if not margins or margins[0] > 0.05:
+            break
+    got = _run_part(backend, "feed_forward", spec, w, x, [70])
+    torch.testing.assert_close(got, want, atol=_tol(backend, want), rtol=0)
+    got = _run_part(backend, "feed_forward", spec, w, x, [3, 1, 40, 26])
+    torch.testing.assert_close(got, want, atol=_tol(backend, want), rtol=0)
+
+
+@pytest.mark.parametrize("backend", BACKENDS)
+@pytest.mark.parametrize("taps,bias,activation,residual", [(4, False, "none", True), (2, True, "silu", False), (1, False, "none", True),
+                                                           (7, True, "none", False)])
+@pytest.mark.parametrize("cuts", [[41], [1, 2, 1, 30, 3, 4], [1] * 41], ids=["whole", "portions", "tokens"])
+def test_short_convolution_alone(backend, taps, bias, activation, residual, cuts):
+    c = 40
+    g = torch.Generator().manual_seed(taps)
+    w = {"f.w": (torch.randn(c, taps, generator=g) * 0.5).bfloat16().float(), "f.b": torch.randn(c, generator=g).bfloat16().float()}
+    x = torch.randn(41, c, generator=g).bfloat16().float()
+    spec = PartSpec("short_conv", {"channels": c, "taps": taps, "weight_name": "w", "bias_name": "b" if bias else None,
+                                   "activation": activation, "residual": residual}, "f.")
+    got = _run_part(backend, "filter", spec, w, x, cuts)
+    want = P.causal_conv(x.double(), w["f.w"].double(), w["f.b"].double() if bias else None)
+    if residual:
+        want = want + x.double()
+    if activation == "silu":
+        want = torch.nn.functional.silu(want)
+    torch.testing.assert_close(got, want.float(), atol=_tol(backend, want.float()), rtol=0)
+
+
+def test_pages_behind_a_block_of_positions_go_back_to_the_pool():
+    """A query never reads before the start of its own block, so the cache manager gives the pages before it back while
+    the request still runs, and promises a running request no more pages than a block and a portion can span."""
+    from serve_b200.parts import CacheNeed
+
+    need = CacheNeed(kv_heads=1, head_dim=16, chunk=24)
+    mgr = CacheManager([need], [None], 8, 32, 2, 512)
+    mgr.open("a")
+    held = []
+    for length in (20, 24, 47, 48, 100, 121):
+        mgr.reserve([("a", length)])
+        mgr.commit("a", length)
+        held.append(mgr.pages_held("a")[0])
+        mgr.check()
+    assert held == [3, 0, 3, 0, 1, 1]        # at 24 and 48 tokens the next query opens a new block: nothing behind it is read again
+    assert mgr.peak_pages(1000, 1) == [(24 + 1 - 2) // 8 + 2]
+    mgr.close("a")
+    assert mgr.groups[0].pool.in_use == 0
