@@ -14,7 +14,7 @@ from serve_b200.engine.step import BatchShape, StepContext
 from serve_b200.parts import build_part
 from tests import helpers
 from tests.plain import rogisun_plain as P
-from tests.rogisun_cases import BACKENDS, CONFIGS, make_engine, make_weights, plain_logits, runtime_for, settled_weights, tolerance, write_model
+from tests.rogisun_cases import BACKENDS, CONFIGS, compare_rows, make_engine, make_weights, plain_logits, runtime_for, settled_weights, tolerance, write_model
 
 LENGTHS = {"p": [1, 5, 23, 49, 75, 130], "q": [2, 9, 31, 64, 101]}
 PAGE = {"p": 8, "q": 16}
@@ -97,7 +97,7 @@ def test_cuts_match_plain(models, name, backend, cut):
     with torch.inference_mode():
         got = helpers.replay(eng, steps)
     eng.kernels.check_errors()
-    helpers.compare_with_plain(got, plain, atol=tolerance(backend, plain))
+    compare_rows(got, plain, backend)
     eng.cache.check()
     assert eng.cache.live == 0
 
@@ -128,7 +128,7 @@ def test_mixed_batches_with_pages_and_slots_used_again(models, name, backend):
     with torch.inference_mode():
         got = helpers.replay(eng, steps)
     eng.kernels.check_errors()
-    helpers.compare_with_plain(got, plain, atol=tolerance(backend, plain))
+    compare_rows(got, plain, backend)
     eng.cache.check()
     assert eng.cache.live == 0 and eng.cache.free_slots == 3
     assert max(g.pool.high_water for g in eng.cache.groups) <= pool
@@ -155,7 +155,7 @@ def test_long_decoding_side_by_side(models, backend):
     eng.kernels.check_errors()
     if backend[0] == "cuda":
         assert eng.stepper.launched_graphs > 80
-    helpers.compare_with_plain(got, plain, atol=tolerance(backend, plain))
+    compare_rows(got, plain, backend)
 
 
 @pytest.mark.parametrize("backend", BACKENDS)
