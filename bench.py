@@ -11,6 +11,11 @@ of three: the way the reference's own benchmark times its generate()); ``prefill
 compares the decode step with the bytes it has to read (every weight once, and the cache of the live requests).
 The weights (2.47 GB) are larger than the L2 cache, so no flush is needed between steps.
 
+``--design rogisun`` is another measurement altogether and leaves the line above as it is: prefill and decode
+throughput of the Rogisun decoder (three layers, one of each mixer, routed experts) at layer sizes of real models,
+beside a Llama decoder of equal width, depth and active feed-forward size, each with the device time of every kernel
+of one prompt step and one decoding step; it prints its own JSON line (see design_bench).
+
 ``--impl reference`` runs limei1221/serve itself, unmodified, from baseline/_ref at the same configuration and prints
 the same line (baseline/reference_arm.py); it imports nothing of serve_b200.
 """
@@ -307,8 +312,114 @@ def float32_points(cfg, args, pk):
                         "peak_tflops": round(fma_tflops, 1), "peak": "SMs x 128 FMA x 2 x max SM clock"}}
 
 
+# ---- another design beside the closest existing one ------------------------------------------------------------------
+DESIGN_SIZES = {
+    # width: (heads of 128, experts, experts per token, expert width)
+    "1024": (8, 32, 2, 512),
+    "2048": (16, 64, 4, 768),
+    "4096": (32, 64, 8, 512),
+}
+
+
+def rogisun_at(width: int, vocab: int = 32000):
+    """A Rogisun configuration with layers of a real model's sizes: one layer of each mixer, experts everywhere."""
+    from serve_b200.config import config_from_dict
+
+    heads, experts, top, ff = DESIGN_SIZES[str(width)]
+    moe = {"kind": "moe", "expert": {"ff": ff, "limit": 7.0}, "router": {"experts": experts, "top": top}}
+    layers = [
+        {"type": "mamba2", "mixer": {"heads": 2 * width // 64, "vdim": 64, "state": 128, "groups": 8, "norm_groups": 8, "conv": 4}, "mlp": moe},
+        {"type": "parallel", "mixer": {
+            "left": {"heads": heads, "kv_heads": max(1, heads // 4), "dim": 128, "vdim": 128, "scale": 128 ** -0.5, "mask": {"size": 1024}},
+            "right": {"heads": heads, "kv_heads": heads, "dim": 128, "vdim": 128, "conv": 4, "rank": 64},
+            "left_scale": 0.5, "right_scale": 0.5}, "mlp": moe},
+        {"type": "lightning", "mixer": {"heads": heads, "dim": 128, "vdim": 128,
+                                        "decay": [1.0 - 2.0 ** (-5.0 - 4.0 * h / heads) for h in range(heads)]}, "mlp": moe},
+    ]
+    return config_from_dict({"architecture": "Rogisun", "width": width, "vocab": vocab, "norm": {"eps": 1e-5}, "canon": {"taps": 4},
+                             "layers": layers, "max_position": CONTEXT})
+
+
+def llama_at(width: int, vocab: int = 32000):
+    """The closest existing model at equal size: as wide, as deep, the same attention heads as the Rogisun attention, and a
+    dense feed-forward as wide as the experts one token goes through."""
+    from serve_b200.config import config_from_dict
+
+    heads, _experts, top, ff = DESIGN_SIZES[str(width)]
+    return config_from_dict({"architectures": ["LlamaForCausalLM"], "hidden_size": width, "num_hidden_layers": 3, "num_attention_heads": heads,
+                             "num_key_value_heads": max(1, heads // 4), "head_dim": 128, "intermediate_size": top * ff, "vocab_size": vocab,
+                             "rms_norm_eps": 1e-5, "rope_theta": 500000.0, "tie_word_embeddings": True, "max_position_embeddings": CONTEXT})
+
+
+def kernel_times(eng, entries, end):
+    """Device time of every kernel of one step, added up by kernel name: [(name, launches, microseconds)], longest first."""
+    import torch
+    from torch.profiler import ProfilerActivity, profile
+
+    with profile(activities=[ProfilerActivity.CUDA]) as prof:
+        eng.step(entries)
+        torch.cuda.synchronize()
+    for rid in end:
+        eng.end(rid)
+    total = {}
+    for e in prof.events():
+        if e.device_type == torch.autograd.DeviceType.CUDA:
+            name = e.name.replace("(anonymous namespace)::", "").replace("void ", "").split("(")[0][:60]
+            n, us = total.get(name, (0, 0.0))
+            total[name] = (n + 1, us + (e.time_range.end - e.time_range.start))
+    return sorted(((k, n, round(us, 1)) for k, (n, us) in total.items()), key=lambda r: -r[2])
+
+
+def design_bench(args):
+    """Prefill (one prompt of 2,048 tokens) and decode (batch 8 after 2,048-token prompts, from CUDA graphs) of Rogisun and of
+    the Llama decoder of equal size, at each width asked for, bfloat16, random weights; CUDA events on the stream, the
+    weights alone exceed the L2 cache. Prints one JSON line: per width and design the two rates and the kernels of one prompt
+    step and one (eager) decoding step with their device times."""
+    import torch
+
+    from serve_b200.config import EngineConfig
+    from serve_b200.engine import Engine, StepEntry
+    from serve_b200.sampling import Sampler
+
+    out = {"design": "rogisun", "beside": "llama of equal width, depth and active feed-forward width", "dtype": "bf16",
+           "data": "synthetic: uniform random token ids, seeded random weights", "prompt_tokens": PREFILL_TOKENS, "decode_batch": args.batch,
+           "decode_context": PROMPT_LEN, "steps": args.steps, "warmup": max(args.warmup, 3), "sizes": {}}
+    batch = args.batch
+    for width in [int(w) for w in args.widths.split(",")]:
+        rec = {}
+        for name, cfg in (("rogisun", rogisun_at(width)), ("llama", llama_at(width))):
+            ec = EngineConfig(dtype="bfloat16", page_size=64, num_pages=(batch + 2) * CONTEXT // 64, max_slots=batch + 2,
+                              max_tokens_per_step=PREFILL_TOKENS, max_context=CONTEXT, use_cuda_graphs=not args.no_graphs)
+            with torch.inference_mode():
+                eng = Engine.from_config(cfg, seed=0, engine_config=ec)
+                sampler = Sampler(eng.kernels, eng.rt.device, seed=0)
+                vocab = eng.spec.vocab_size
+                pre_ms = prefill_bench(eng, vocab, reps=5, seed=7)
+                ms, _ctx, launches, lib_calls = decode_bench(eng, sampler, batch, args.steps, max(args.warmup, 3), vocab, seed=1)
+                g = torch.Generator().manual_seed(5)
+                toks = torch.randint(0, vocab, (PREFILL_TOKENS,), generator=g).tolist()
+                prompt_kernels = kernel_times(eng, [StepEntry("k", toks, [PREFILL_TOKENS - 1])], [])
+                eng.stepper.use_cuda_graphs = False
+                rids = ["k"] + [f"k{i}" for i in range(1, batch)]
+                for rid in rids[1:]:
+                    eng.step([StepEntry(rid, toks[:PROMPT_LEN - 8], [])])
+                decode_kernels = kernel_times(eng, [StepEntry(rid, [1], [0]) for rid in rids], rids)
+            rec[name] = {"prefill_tokens_per_s": round(PREFILL_TOKENS / (pre_ms * 1e-3), 1), "prefill_ms": round(pre_ms, 3),
+                         "decode_tokens_per_s": round(batch * 1000.0 / ms, 1), "decode_ms_per_step": round(ms, 4),
+                         "gpu_launches": int(launches), "library_gemm_calls": int(lib_calls),
+                         "prompt_step_kernels": prompt_kernels[:14], "decode_step_kernels": decode_kernels[:14]}
+            del eng, sampler
+            torch.cuda.empty_cache()
+        out["sizes"][str(width)] = rec
+    print(json.dumps(out))
+    return 0
+
+
 def main():
     ap = argparse.ArgumentParser()
+    ap.add_argument("--design", default=None, choices=["rogisun"],
+                    help="measure this design beside the Llama decoder of equal size instead of the headline workload")
+    ap.add_argument("--widths", default="1024,2048,4096", help="with --design: layer widths to measure")
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=128)
     ap.add_argument("--warmup", type=int, default=8)
@@ -329,6 +440,8 @@ def main():
     if args.impl == "reference":
         return reference_arm(args)
     args.warmup = max(args.warmup, 3)
+    if args.design:
+        return design_bench(args)
 
     import dataclasses
 

@@ -54,12 +54,13 @@ __global__ void __launch_bounds__(128) moe_route_kernel(const float* __restrict_
   }
 }
 
-constexpr int TM = 32;            // rows of a tile
+constexpr int TM = 32;            // rows of a tile of the plain-arithmetic products (the tensor-core ones take MB_M)
 
 // One block. order[offsets[e] .. offsets[e+1]) = the pairs of expert e; tiles: (expert, first row) for every TM rows
 // of an expert's group, n_tiles[0] of them.
-__global__ void __launch_bounds__(1024) moe_sort_kernel(const int* __restrict__ idx, int n_pairs, int E, int* __restrict__ offsets,
-                                                        int* __restrict__ order, int* __restrict__ tiles, int* __restrict__ n_tiles) {
+__global__ void __launch_bounds__(1024) moe_sort_kernel(const int* __restrict__ idx, int n_pairs, int E, int tile_rows,
+                                                        int* __restrict__ offsets, int* __restrict__ order, int* __restrict__ tiles,
+                                                        int* __restrict__ n_tiles) {
   extern __shared__ int sh[];
   int* count = sh;            // [E]
   int* start = sh + E;        // [E + 1]
@@ -75,7 +76,7 @@ __global__ void __launch_bounds__(1024) moe_sort_kernel(const int* __restrict__ 
     for (int e = 0; e < E; ++e) {
       start[e] = at;
       offsets[e] = at;
-      for (int r0 = 0; r0 < count[e]; r0 += TM) {
+      for (int r0 = 0; r0 < count[e]; r0 += tile_rows) {
         tiles[2 * nt] = e;
         tiles[2 * nt + 1] = at + r0;
         ++nt;
@@ -233,6 +234,187 @@ __global__ void __launch_bounds__(MOE_THREADS) moe_down_kernel(const T* __restri
   }
 }
 
+
+// ------------------------------------------------------------------------------------------ bfloat16 on tensor cores
+// The same two products with mma.sync m16n8k16 (bfloat16 in, float accumulators): tiles of MB_M rows x 64 columns,
+// k in steps of 32 through a three-stage cp.async ring, four warps as 2 x 2, each 32 rows x 32 columns. Rows of the
+// shared tiles are 80 bytes apart, so the eight 16-byte rows an ldmatrix reads fall into different banks. For
+// gate/up a block's 64 columns are 32 gate columns and the 32 up columns of the same outputs, and a warp takes 16 of
+// each, so a thread holds the gate and the up sum of the same output and applies the activation itself.
+constexpr int MB_M = 64, MB_N = 64, MB_K = 32, MB_STAGES = 3, MB_LD = MB_K + 8, MB_THREADS = 128;
+
+__device__ __forceinline__ void cp_async16(void* smem, const void* gmem, bool valid) {
+  const unsigned s = (unsigned)__cvta_generic_to_shared(smem);
+  const int n = valid ? 16 : 0;                       // 0: nothing is read, the 16 bytes are filled with zeros
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(s), "l"(gmem), "r"(n));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;"); }
+template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N)); }
+__device__ __forceinline__ void ldmatrix_x4(unsigned (&r)[4], const void* p) {
+  const unsigned s = (unsigned)__cvta_generic_to_shared(p);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(s));
+}
+__device__ __forceinline__ void mma_bf16(float (&c)[4], const unsigned (&a)[4], unsigned b0, unsigned b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3]) : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+// One k-loop for both products. a_row(m): global pointer of row m of the A tile at k = 0 (null: a row of zeros);
+// b_row(n): the same for row n of the B tile (a weight row); any_global: an address in global memory for the copies that
+// read nothing. acc[i][j]: rows wm * 32 + i * 16 (+8), columns wn * 32 + j * 8.
+template <typename ARow, typename BRow>
+__device__ __forceinline__ void mma_tile_loop(ARow a_row, BRow b_row, const __nv_bfloat16* any_global, int K, __nv_bfloat16* smem,
+                                              float (&acc)[2][4][4]) {
+  typedef __nv_bfloat16 B;
+  B* As = smem;                                     // [stages][MB_M][MB_LD]
+  B* Bs = smem + MB_STAGES * MB_M * MB_LD;          // [stages][MB_N][MB_LD]
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int wm = warp >> 1, wn = warp & 1;
+  // this thread's two 16-byte pieces of each tile: rows r0 and r0 + 32, piece (tid & 3) of the row's four
+  const int r0 = tid >> 2, piece = (tid & 3) * 8;
+  const B* a_src[2] = {a_row(r0), a_row(r0 + 32)};
+  const B* b_src[2] = {b_row(r0), b_row(r0 + 32)};
+  auto load = [&](int stage, int k0) {
+#pragma unroll
+    for (int u = 0; u < 2; ++u) {
+      const int row = r0 + 32 * u;
+      cp_async16(As + ((size_t)stage * MB_M + row) * MB_LD + piece, a_src[u] ? a_src[u] + k0 + piece : any_global, a_src[u] != nullptr);
+      cp_async16(Bs + ((size_t)stage * MB_N + row) * MB_LD + piece, b_src[u] ? b_src[u] + k0 + piece : any_global, b_src[u] != nullptr);
+    }
+  };
+  const int nk = K / MB_K;
+#pragma unroll
+  for (int s = 0; s < MB_STAGES - 1; ++s) {
+    if (s < nk) load(s, s * MB_K);
+    cp_async_commit();
+  }
+  for (int kt = 0; kt < nk; ++kt) {
+    cp_async_wait<MB_STAGES - 2>();
+    __syncthreads();                                 // tile kt is there, and every warp is done with tile kt - 1
+    const int nxt = kt + MB_STAGES - 1;
+    if (nxt < nk) load(nxt % MB_STAGES, nxt * MB_K);
+    cp_async_commit();
+    const B* at = As + (size_t)(kt % MB_STAGES) * MB_M * MB_LD;
+    const B* bt = Bs + (size_t)(kt % MB_STAGES) * MB_N * MB_LD;
+#pragma unroll
+    for (int kk = 0; kk < MB_K; kk += 16) {
+      unsigned af[2][4], bf[2][4];
+#pragma unroll
+      for (int i = 0; i < 2; ++i)      // 16 x 16 of A: lanes 0-15 rows 0-15 at k, lanes 16-31 the same rows at k + 8
+        ldmatrix_x4(af[i], at + (size_t)(wm * 32 + i * 16 + (lane & 15)) * MB_LD + kk + (lane >> 4) * 8);
+#pragma unroll
+      for (int j = 0; j < 2; ++j)      // 16 columns x 16 of k: matrices (n 0-7, k), (n 0-7, k + 8), (n 8-15, k), (n 8-15, k + 8)
+        ldmatrix_x4(bf[j], bt + (size_t)(wn * 32 + j * 16 + (lane & 7) + ((lane >> 4) << 3)) * MB_LD + kk + ((lane >> 3) & 1) * 8);
+#pragma unroll
+      for (int i = 0; i < 2; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) mma_bf16(acc[i][j], af[i], bf[j >> 1][(j & 1) * 2], bf[j >> 1][(j & 1) * 2 + 1]);
+    }
+  }
+  cp_async_wait<0>();
+}
+
+constexpr size_t MB_SMEM = (size_t)MB_STAGES * (MB_M + MB_N) * MB_LD * sizeof(__nv_bfloat16);
+
+// grid (ceil(ff / 32), row tiles of MB_M rows). Tile rows of the B tile: warp column wn takes rows wn * 32 .. + 31 =
+// 16 gate rows (outputs n0 + wn * 16 ..) and then the 16 up rows of the same outputs.
+__global__ void __launch_bounds__(MB_THREADS) moe_gate_up_mma_kernel(
+    const __nv_bfloat16* __restrict__ x, int x_stride, const __nv_bfloat16* __restrict__ w_gu, const int* __restrict__ order,
+    const int* __restrict__ offsets, const int* __restrict__ tiles, const int* __restrict__ n_tiles, const float* __restrict__ wts,
+    int top, int K, int ff, int scale_input, int act_kind, float limit, float alpha, __nv_bfloat16* __restrict__ act) {
+  if ((int)blockIdx.y >= n_tiles[0]) return;
+  extern __shared__ __align__(16) unsigned char raw[];
+  __nv_bfloat16* smem = (__nv_bfloat16*)raw;
+  __shared__ int tok[MB_M];
+  __shared__ float rw[MB_M];
+  const int e = tiles[2 * blockIdx.y], row0 = tiles[2 * blockIdx.y + 1];
+  const int rows = min(MB_M, offsets[e + 1] - row0);
+  const int n0 = blockIdx.x * 32;
+  const int tid = threadIdx.x;
+  if (tid < MB_M) {
+    const int pair = tid < rows ? order[row0 + tid] : -1;
+    tok[tid] = pair >= 0 ? pair / top : -1;
+    rw[tid] = pair >= 0 ? wts[pair] : 0.f;
+  }
+  __syncthreads();
+  const __nv_bfloat16* wg = w_gu + (size_t)e * 2 * ff * K;
+  float acc[2][4][4] = {};
+  mma_tile_loop(
+      [&](int m) -> const __nv_bfloat16* { return tok[m] >= 0 ? x + (size_t)tok[m] * x_stride : nullptr; },
+      [&](int n) -> const __nv_bfloat16* {
+        const int wn = n >> 5, within = n & 31;
+        const int col = n0 + wn * 16 + (within & 15);
+        if (col >= ff) return nullptr;
+        return wg + ((size_t)(within >> 4) * ff + col) * K;           // within >= 16: the up row of that output
+      },
+      wg, K, smem, acc);
+  const int lane = tid & 31, warp = tid >> 5, wm = warp >> 1, wn = warp & 1;
+#pragma unroll
+  for (int i = 0; i < 2; ++i)
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+      const int m = wm * 32 + i * 16 + (lane >> 2) + half * 8;
+      if (m >= rows) continue;
+      const float sc = scale_input ? rw[m] : 1.f;
+#pragma unroll
+      for (int j = 0; j < 2; ++j)
+#pragma unroll
+        for (int c = 0; c < 2; ++c) {
+          const int col = n0 + wn * 16 + j * 8 + (lane & 3) * 2 + c;
+          if (col >= ff) continue;
+          float g = acc[i][j][half * 2 + c] * sc, u = acc[i][j + 2][half * 2 + c] * sc, yv;
+          if (act_kind == 1) {
+            g = fminf(g, limit);
+            u = fminf(fmaxf(u, -limit), limit);
+            yv = g * sigmoid_f(alpha * g) * (u + 1.f);
+          } else {
+            yv = g * sigmoid_f(g) * u;
+          }
+          act[(size_t)(row0 + m) * ff + col] = __float2bfloat16_rn(yv);
+        }
+    }
+}
+
+// grid (ceil(N / 64), row tiles).
+template <typename O>
+__global__ void __launch_bounds__(MB_THREADS) moe_down_mma_kernel(const __nv_bfloat16* __restrict__ act, const __nv_bfloat16* __restrict__ w_down,
+                                                                  const int* __restrict__ order, const int* __restrict__ offsets,
+                                                                  const int* __restrict__ tiles, const int* __restrict__ n_tiles,
+                                                                  const float* __restrict__ wts, int ff, int N, int scale_output,
+                                                                  O* __restrict__ out) {
+  if ((int)blockIdx.y >= n_tiles[0]) return;
+  extern __shared__ __align__(16) unsigned char raw[];
+  __nv_bfloat16* smem = (__nv_bfloat16*)raw;
+  __shared__ int pair_of[MB_M];
+  const int e = tiles[2 * blockIdx.y], row0 = tiles[2 * blockIdx.y + 1];
+  const int rows = min(MB_M, offsets[e + 1] - row0);
+  const int n0 = blockIdx.x * MB_N;
+  const int tid = threadIdx.x;
+  if (tid < MB_M) pair_of[tid] = tid < rows ? order[row0 + tid] : -1;
+  __syncthreads();
+  const __nv_bfloat16* w = w_down + (size_t)e * N * ff;
+  float acc[2][4][4] = {};
+  mma_tile_loop([&](int m) -> const __nv_bfloat16* { return m < rows ? act + (size_t)(row0 + m) * ff : nullptr; },
+                [&](int n) -> const __nv_bfloat16* { return n0 + n < N ? w + (size_t)(n0 + n) * ff : nullptr; }, w, ff, smem, acc);
+  const int lane = tid & 31, warp = tid >> 5, wm = warp >> 1, wn = warp & 1;
+#pragma unroll
+  for (int i = 0; i < 2; ++i)
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+      const int m = wm * 32 + i * 16 + (lane >> 2) + half * 8;
+      if (m >= rows) continue;
+      const int pair = pair_of[m];
+      const float sc = scale_output ? wts[pair] : 1.f;
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+#pragma unroll
+        for (int c = 0; c < 2; ++c) {
+          const int col = n0 + wn * 32 + j * 8 + (lane & 3) * 2 + c;
+          if (col < N) out[(size_t)pair * N + col] = from_float<O>(acc[i][j][half * 2 + c] * sc);
+        }
+    }
+}
+
 template <typename T>
 __global__ void __launch_bounds__(256) moe_combine_kernel(const float* __restrict__ parts, int top, int N, long long total,
                                                           T* __restrict__ out) {
@@ -247,7 +429,12 @@ __global__ void __launch_bounds__(256) moe_combine_kernel(const float* __restric
 
 }  // namespace
 
-SB_EXPORT int sb_moe_tile_rows() { return TM; }
+// Rows of a tile for a step's products: the tensor-core kernels (bfloat16, k a multiple of 32 and rows 16-byte aligned on
+// both products) take 64, the plain ones 32. The grouping (sb_moe_sort) and both products must be given the same answer.
+SB_EXPORT int sb_moe_tile_rows(int dtype, int K, int ff, int x_stride) {
+  const bool mma = dtype == SB_DTYPE_BF16 && K % MB_K == 0 && ff % MB_K == 0 && x_stride % 8 == 0;
+  return mma ? MB_M : TM;
+}
 
 // logits float [T, E] -> idx int32 [T, top], wts float [T, top]. score_kind 0: sigmoid of the logit, 1: softmax over the
 // experts; renorm: the chosen weights divided by their sum.
@@ -260,11 +447,12 @@ SB_EXPORT int sb_moe_route(const float* logits, int E, int top, int score_kind, 
   return 0;
 }
 
-// idx int32 [n_pairs] -> offsets [E + 1], order [n_pairs], tiles [2 * (n_pairs / TM + E)], n_tiles [1].
-SB_EXPORT int sb_moe_sort(const int* idx, int n_pairs, int E, int* offsets, int* order, int* tiles, int* n_tiles, cudaStream_t stream) {
+// idx int32 [n_pairs] -> offsets [E + 1], order [n_pairs], tiles [2 * (n_pairs / tile_rows + E)], n_tiles [1].
+SB_EXPORT int sb_moe_sort(const int* idx, int n_pairs, int E, int tile_rows, int* offsets, int* order, int* tiles, int* n_tiles,
+                          cudaStream_t stream) {
   if (n_pairs <= 0) return 0;
-  if (E <= 0 || E > 4096) return SB_ERR_LIMIT;
-  moe_sort_kernel<<<1, 1024, (size_t)(2 * E + 1) * sizeof(int), stream>>>(idx, n_pairs, E, offsets, order, tiles, n_tiles);
+  if (E <= 0 || E > 4096 || tile_rows <= 0) return SB_ERR_LIMIT;
+  moe_sort_kernel<<<1, 1024, (size_t)(2 * E + 1) * sizeof(int), stream>>>(idx, n_pairs, E, tile_rows, offsets, order, tiles, n_tiles);
   SB_LAUNCH_CHECK();
   return 0;
 }
@@ -273,8 +461,18 @@ SB_EXPORT int sb_moe_gate_up(const void* x, int x_stride, const void* w_gu, cons
                              const int* n_tiles, const float* wts, int top, int n_pairs, int E, int K, int ff, int scale_input,
                              int act_kind, float limit, float alpha, void* act, int dtype, cudaStream_t stream) {
   if (n_pairs <= 0) return 0;
-  const int max_tiles = n_pairs / TM + (E < n_pairs ? E : n_pairs);
+  const int tile_rows = sb_moe_tile_rows(dtype, K, ff, x_stride);
+  const int max_tiles = n_pairs / tile_rows + (E < n_pairs ? E : n_pairs);
   if (max_tiles > 65535) return SB_ERR_LIMIT;
+  if (tile_rows == MB_M) {
+    if (!aligned16(x) || !aligned16(w_gu)) return SB_ERR_ALIGN;
+    cudaFuncSetAttribute(moe_gate_up_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)MB_SMEM);
+    moe_gate_up_mma_kernel<<<dim3((ff + 31) / 32, max_tiles), MB_THREADS, MB_SMEM, stream>>>(
+        (const __nv_bfloat16*)x, x_stride, (const __nv_bfloat16*)w_gu, order, offsets, tiles, n_tiles, wts, top, K, ff, scale_input,
+        act_kind, limit, alpha, (__nv_bfloat16*)act);
+    SB_LAUNCH_CHECK();
+    return 0;
+  }
   dim3 grid((ff + GU_COLS - 1) / GU_COLS, max_tiles);
   if (dtype == SB_DTYPE_F32)
     moe_gate_up_kernel<float><<<grid, MOE_THREADS, 0, stream>>>((const float*)x, x_stride, (const float*)w_gu, order, offsets, tiles,
@@ -292,10 +490,30 @@ SB_EXPORT int sb_moe_gate_up(const void* x, int x_stride, const void* w_gu, cons
 // out: [n_pairs, N] of dtype out_dtype (float for rows that are still to be added up).
 SB_EXPORT int sb_moe_down(const void* act, const void* w_down, const int* order, const int* offsets, const int* tiles, const int* n_tiles,
                           const float* wts, int n_pairs, int E, int ff, int N, int scale_output, void* out, int dtype, int out_dtype,
-                          cudaStream_t stream) {
+                          int tile_rows, cudaStream_t stream) {
   if (n_pairs <= 0) return 0;
-  const int max_tiles = n_pairs / TM + (E < n_pairs ? E : n_pairs);
+  if (tile_rows != TM && tile_rows != MB_M) return SB_ERR_SHAPE;
+  const int max_tiles = n_pairs / tile_rows + (E < n_pairs ? E : n_pairs);
   if (max_tiles > 65535) return SB_ERR_LIMIT;
+  if (tile_rows == MB_M) {
+    if (dtype != SB_DTYPE_BF16 || ff % MB_K) return SB_ERR_SHAPE;
+    if (!aligned16(act) || !aligned16(w_down)) return SB_ERR_ALIGN;
+    dim3 mgrid((N + MB_N - 1) / MB_N, max_tiles);
+    if (out_dtype == SB_DTYPE_BF16) {
+      cudaFuncSetAttribute(moe_down_mma_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)MB_SMEM);
+      moe_down_mma_kernel<__nv_bfloat16><<<mgrid, MB_THREADS, MB_SMEM, stream>>>(
+          (const __nv_bfloat16*)act, (const __nv_bfloat16*)w_down, order, offsets, tiles, n_tiles, wts, ff, N, scale_output,
+          (__nv_bfloat16*)out);
+    } else if (out_dtype == SB_DTYPE_F32) {
+      cudaFuncSetAttribute(moe_down_mma_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)MB_SMEM);
+      moe_down_mma_kernel<float><<<mgrid, MB_THREADS, MB_SMEM, stream>>>((const __nv_bfloat16*)act, (const __nv_bfloat16*)w_down, order,
+                                                                          offsets, tiles, n_tiles, wts, ff, N, scale_output, (float*)out);
+    } else {
+      return SB_ERR_DTYPE;
+    }
+    SB_LAUNCH_CHECK();
+    return 0;
+  }
   dim3 grid((N + DN_COLS - 1) / DN_COLS, max_tiles);
   if (dtype == SB_DTYPE_F32 && out_dtype == SB_DTYPE_F32)
     moe_down_kernel<float, float><<<grid, MOE_THREADS, 0, stream>>>((const float*)act, (const float*)w_down, order, offsets, tiles, n_tiles,

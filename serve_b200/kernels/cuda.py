@@ -671,7 +671,8 @@ class CudaKernels:
         ff, n, k = w_down.shape[2], w_down.shape[1], h.shape[1]
         pairs = t * top
         dev = h.device
-        max_tiles = pairs // lib.sb_moe_tile_rows() + min(e, pairs)
+        tile_rows = lib.sb_moe_tile_rows(_DT[h.dtype], k, ff, h.stride(0))     # 64 on the tensor-core kernels, else 32
+        max_tiles = pairs // tile_rows + min(e, pairs)
         ints = torch.empty(2 * pairs + e + 1 + 2 * max_tiles + 1, dtype=torch.int32, device=dev)
         idx, order = ints[:pairs], ints[pairs: 2 * pairs]
         offsets = ints[2 * pairs: 2 * pairs + e + 1]
@@ -682,14 +683,14 @@ class CudaKernels:
         self.launches += 4
         _check(lib.sb_moe_route(_p(logits), e, top, {"sigmoid": 0, "softmax": 1}[score], 1 if renormalise else 0, t, _p(idx), _p(wts), s),
                "expert choice")
-        _check(lib.sb_moe_sort(_p(idx), pairs, e, _p(offsets), _p(order), _p(tiles), _p(n_tiles), s), "grouping by expert")
+        _check(lib.sb_moe_sort(_p(idx), pairs, e, tile_rows, _p(offsets), _p(order), _p(tiles), _p(n_tiles), s), "grouping by expert")
         act = torch.empty((pairs, ff), dtype=h.dtype, device=dev)
         _check(lib.sb_moe_gate_up(_p(h), h.stride(0), _p(w_gate_up), _p(order), _p(offsets), _p(tiles), _p(n_tiles), _p(wts), top, pairs,
                                   e, k, ff, 1 if scale_input else 0, {"swiglu": 0, "clamped_swish": 1}[activation],
                                   ctypes.c_float(limit), ctypes.c_float(alpha), _p(act), _DT[h.dtype], s), "experts, gate and up")
         parts = out if top == 1 else torch.empty((pairs, n), dtype=torch.float32, device=dev)
         _check(lib.sb_moe_down(_p(act), _p(w_down), _p(order), _p(offsets), _p(tiles), _p(n_tiles), _p(wts), pairs, e, ff, n,
-                               0 if scale_input else 1, _p(parts), _DT[h.dtype], _DT[parts.dtype], s), "experts, down")
+                               0 if scale_input else 1, _p(parts), _DT[h.dtype], _DT[parts.dtype], tile_rows, s), "experts, down")
         if top > 1:
             self.launches += 1
             _check(lib.sb_moe_combine(_p(parts), top, t, n, _p(out), _DT[out.dtype], s), "sum over a token's experts")

@@ -204,7 +204,7 @@ def _run_part(backend, family, spec, weights, x, cuts, page=8):
     names = {d.name for d in part.tensor_decls()}
     part.load({n: weights[n].to(dev).to(rt.act_dtype) for n in names})
     need = part.cache_need() if hasattr(part, "cache_need") else None
-    mgr = CacheManager([need], [None], page, 64, 1, 256, device=dev, kv_dtype=rt.act_dtype)
+    mgr = CacheManager([need], [None], page, 64, 1, 512, device=dev, kv_dtype=rt.act_dtype)
     view = mgr.views()[0]
 
     def call(h, ctx):
@@ -356,6 +356,29 @@ def test_routed_experts_alone(backend, name, index):
     torch.testing.assert_close(got, want, atol=_tol(backend, want), rtol=0)
     got = _run_part(backend, "feed_forward", spec, w, x, [3, 1, 40, 26])
     torch.testing.assert_close(got, want, atol=_tol(backend, want), rtol=0)
+
+
+@pytest.mark.parametrize("backend", BACKENDS)
+@pytest.mark.parametrize("top,ff,width", [(2, 96, 128), (1, 64, 160), (4, 40, 96)])
+def test_routed_experts_with_many_tokens_per_expert(backend, top, ff, width):
+    """Hundreds of tokens over six experts: an expert's rows fill several tiles and the last one partly; with widths that are
+    multiples of 32 the bfloat16 products run on the tensor-core kernels, otherwise on the plain ones."""
+    layer = {"kind": "moe", "expert": {"ff": ff, "limit": 1.2}, "router": {"experts": 6, "top": top}}
+    g = torch.Generator().manual_seed(top)
+    rnd = lambda *shape, s=1.0: (torch.randn(*shape, generator=g) * s).bfloat16().float()
+    w = {"m.router": rnd(6, width, s=6.0 / width ** 0.5)}
+    for e in range(6):
+        w[f"m.e{e}.gate"], w[f"m.e{e}.up"], w[f"m.e{e}.down"] = rnd(ff, width, s=width ** -0.5), rnd(ff, width, s=width ** -0.5), rnd(width, ff, s=ff ** -0.5)
+    w["m.router"][0] += 0.4 * w["m.router"][1]                 # an uneven load: expert 0 gets more than its share
+    x = rnd(333, width)
+    margins = []
+    want = P.routed_experts(x.double(), {k: v.double() for k, v in w.items()}, "m.", layer, margins).float()
+    close = (torch.sort(x.double() @ w["m.router"].double().T, descending=True).values[:, top - 1:top + 1].diff(dim=1).abs() < 0.08).flatten()
+    spec = PartSpec("routed_experts", {"hidden": width, "experts": 6, "top": top, "ff": ff, "limit": 1.2}, "m.")
+    got = _run_part(backend, "feed_forward", spec, w, x, [333])
+    keep = ~close                                               # rows whose choice of experts is no close call
+    assert int(keep.sum()) > 250
+    torch.testing.assert_close(got[keep], want[keep], atol=_tol(backend, want), rtol=0)
 
 
 @pytest.mark.parametrize("backend", BACKENDS)
