@@ -21,36 +21,65 @@ __device__ __forceinline__ float sigmoid_f(float x) { return 1.f / (1.f + expf(-
 
 constexpr int ROUTE_MAX_TOP = 16;
 
-// One thread per token: E is small, and the scores are read once.
+// A warp per token: lane l holds the logits of experts l, l + 32, ... (at most ROUTE_PER_LANE of them); the best of
+// what is left is found `top` times by a shuffle tree over (logit, index), lower index first on equal logits.
+constexpr int ROUTE_PER_LANE = 32;      // so at most 1024 experts
+
 __global__ void __launch_bounds__(128) moe_route_kernel(const float* __restrict__ logits, int E, int top, int score_kind, int renorm,
                                                         int n_tokens, int* __restrict__ idx, float* __restrict__ wts) {
-  const int t = blockIdx.x * blockDim.x + threadIdx.x;
+  const int lane = threadIdx.x & 31;
+  const int t = blockIdx.x * 4 + (threadIdx.x >> 5);
   if (t >= n_tokens) return;
   const float* z = logits + (size_t)t * E;
-  int best[ROUTE_MAX_TOP];
-  float val[ROUTE_MAX_TOP];
-  float zmax = -INFINITY, denom = 1.f;
+  float mine[ROUTE_PER_LANE];
+  float zmax = -INFINITY;
+#pragma unroll
+  for (int u = 0; u < ROUTE_PER_LANE; ++u) {
+    const int e = lane + 32 * u;
+    mine[u] = e < E ? z[e] : -INFINITY;
+    zmax = fmaxf(zmax, mine[u]);
+  }
+  float denom = 1.f;
   if (score_kind == 1) {                        // softmax over all experts
-    for (int e = 0; e < E; ++e) zmax = fmaxf(zmax, z[e]);
-    denom = 0.f;
-    for (int e = 0; e < E; ++e) denom += expf(z[e] - zmax);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) zmax = fmaxf(zmax, __shfl_xor_sync(0xffffffffu, zmax, o));
+    float part = 0.f;
+#pragma unroll
+    for (int u = 0; u < ROUTE_PER_LANE; ++u)
+      if (lane + 32 * u < E) part += expf(mine[u] - zmax);
+    denom = warp_sum(part);
   }
+  float val = 0.f, total = 0.f;                 // lane s keeps the s-th choice
+  int chosen = -1;
   for (int s = 0; s < top; ++s) {
-    int arg = -1;
     float m = -INFINITY;
-    for (int e = 0; e < E; ++e) {
-      bool taken = false;
-      for (int u = 0; u < s; ++u) taken |= best[u] == e;
-      if (!taken && (arg < 0 || z[e] > m)) { m = z[e]; arg = e; }      // the scores are monotone in the logits
+    int arg = 0x7fffffff;
+#pragma unroll
+    for (int u = 0; u < ROUTE_PER_LANE; ++u) {
+      const int e = lane + 32 * u;
+      if (e < E && (mine[u] > m || (mine[u] == m && e < arg)) && mine[u] != -INFINITY) { m = mine[u]; arg = e; }
     }
-    best[s] = arg;
-    val[s] = score_kind == 1 ? expf(m - zmax) / denom : sigmoid_f(m);
+    if (arg == 0x7fffffff) {                     // nothing left in this lane (or only minus infinity): offer its first free slot last
+      m = -INFINITY;
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float om = __shfl_xor_sync(0xffffffffu, m, o);
+      const int oa = __shfl_xor_sync(0xffffffffu, arg, o);
+      if (om > m || (om == m && oa < arg)) { m = om; arg = oa; }
+    }
+    if (arg != 0x7fffffff && (arg & 31) == lane) {
+#pragma unroll
+      for (int u = 0; u < ROUTE_PER_LANE; ++u)
+        if (u == (arg >> 5)) mine[u] = -INFINITY;    // taken
+    }
+    const float v = score_kind == 1 ? expf(m - zmax) / denom : sigmoid_f(m);
+    total += v;
+    if (lane == s) { val = v; chosen = arg == 0x7fffffff ? 0 : arg; }
   }
-  float total = 0.f;
-  for (int s = 0; s < top; ++s) total += val[s];
-  for (int s = 0; s < top; ++s) {
-    idx[(size_t)t * top + s] = best[s];
-    wts[(size_t)t * top + s] = renorm ? val[s] / total : val[s];
+  if (lane < top) {
+    idx[(size_t)t * top + lane] = chosen;
+    wts[(size_t)t * top + lane] = renorm ? val / total : val;
   }
 }
 
@@ -441,8 +470,8 @@ SB_EXPORT int sb_moe_tile_rows(int dtype, int K, int ff, int x_stride) {
 SB_EXPORT int sb_moe_route(const float* logits, int E, int top, int score_kind, int renorm, int n_tokens, int* idx, float* wts,
                            cudaStream_t stream) {
   if (n_tokens <= 0) return 0;
-  if (E <= 0 || top <= 0 || top > E || top > ROUTE_MAX_TOP) return SB_ERR_LIMIT;
-  moe_route_kernel<<<(n_tokens + 127) / 128, 128, 0, stream>>>(logits, E, top, score_kind, renorm, n_tokens, idx, wts);
+  if (E <= 0 || top <= 0 || top > E || top > ROUTE_MAX_TOP || E > 32 * ROUTE_PER_LANE) return SB_ERR_LIMIT;
+  moe_route_kernel<<<(n_tokens + 3) / 4, 128, 0, stream>>>(logits, E, top, score_kind, renorm, n_tokens, idx, wts);
   SB_LAUNCH_CHECK();
   return 0;
 }

@@ -56,6 +56,56 @@ __global__ void __launch_bounds__(CONV_THREADS) causal_conv_kernel(
   }
 }
 
+// The same for eight neighbouring channels a thread, fetched 16 bytes at a time (bfloat16 with every row start and the
+// channel count a multiple of eight); the arithmetic per channel is the one above, in the same order.
+__global__ void __launch_bounds__(CONV_THREADS) causal_conv8_kernel(
+    const __nv_bfloat16* __restrict__ x, int x_stride, const __nv_bfloat16* __restrict__ w, const __nv_bfloat16* __restrict__ bias,
+    float* __restrict__ state, const int* __restrict__ slots, const int* __restrict__ cu_q, const int* __restrict__ token_row,
+    __nv_bfloat16* __restrict__ out, int out_stride, int C, int taps, int act, int residual, int inline_state) {
+  const int c = (blockIdx.x * CONV_THREADS + threadIdx.x) * 8;
+  const int t = blockIdx.y;
+  if (c >= C) return;
+  const int r = token_row[t];
+  const int i = t - cu_q[r];
+  const int K = taps - 1;
+  float* st = state + (size_t)slots[r] * K * C + c;
+  float acc[8], cur[8];
+#pragma unroll
+  for (int e = 0; e < 8; ++e) { acc[e] = bias ? to_float(bias[c + e]) : 0.f; cur[e] = 0.f; }
+  for (int j = 0; j < taps; ++j) {
+    const int src = i - K + j;
+    if (src >= 0) {
+      const uint4 raw = *reinterpret_cast<const uint4*>(x + (size_t)(t - K + j) * x_stride + c);
+      const __nv_bfloat16* v = reinterpret_cast<const __nv_bfloat16*>(&raw);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) cur[e] = to_float(v[e]);
+    } else {
+      const float4 a = *reinterpret_cast<const float4*>(st + (size_t)(K + src) * C), b = *reinterpret_cast<const float4*>(st + (size_t)(K + src) * C + 4);
+      cur[0] = a.x; cur[1] = a.y; cur[2] = a.z; cur[3] = a.w; cur[4] = b.x; cur[5] = b.y; cur[6] = b.z; cur[7] = b.w;
+    }
+#pragma unroll
+    for (int e = 0; e < 8; ++e) acc[e] += to_float(w[(size_t)(c + e) * taps + j]) * cur[e];
+  }
+  uint4 packed;
+  __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(&packed);
+#pragma unroll
+  for (int e = 0; e < 8; ++e) {
+    float v = acc[e];
+    if (residual) v += cur[e];
+    if (act == 1) v = silu_f(v);
+    o[e] = __float2bfloat16_rn(v);
+  }
+  *reinterpret_cast<uint4*>(out + (size_t)t * out_stride + c) = packed;
+  if (inline_state) {
+    for (int m = 0; m + 1 < K; ++m)
+#pragma unroll
+      for (int e = 0; e < 8; ++e) st[(size_t)m * C + e] = st[(size_t)(m + 1) * C + e];
+    if (K > 0)
+#pragma unroll
+      for (int e = 0; e < 8; ++e) st[(size_t)(K - 1) * C + e] = cur[e];
+  }
+}
+
 // After a step: the state of row r becomes its last taps - 1 inputs (older ones come from the old state when the
 // portion is shorter than that). One thread per (row, channel) reads all it needs before it writes.
 template <typename T>
@@ -86,15 +136,19 @@ __global__ void __launch_bounds__(CONV_THREADS) conv_state_kernel(const T* __res
 //   S <- a * S;   u = v                      (MODE_DECAY, MODE_SSM: u = dt * x)
 //                 u = beta * (v - S^T k)     (MODE_DELTA)
 //   S <- S + k u^T;   o = S^T q  (+ D * x for MODE_SSM)
-// The columns of S never meet, so a block takes (request, head, a slice of columns) and walks the row's tokens in
-// order. A thread keeps REC_RPT rows of one column in registers (rows part, part + P, ...; P lanes share a column
-// and add their parts by shuffles), so dk <= 32 * REC_RPT. Tokens are staged through shared memory REC_TS at a
-// time; what each mode does to its inputs on the way (silu; softplus and exponentials; unit vectors) happens
-// there, in float.
+// Two kernels. The first works on every (token, head) at once and leaves, as float, what the walk over the tokens
+// reads: q and k (after silu, or as unit vectors), the decays (after softplus and the exponentials), the values and
+// the per-token factor (dt or beta). The second walks: the columns of S never meet, so a block takes (request, head, a
+// slice of columns) and goes through the row's tokens in order. A thread keeps REC_RPT rows of one column in
+// registers; P lanes share a column and add their parts by shuffles, so dk <= 32 * REC_RPT. Rows are padded to
+// dkp = REC_RPT * P with k = q = 0, which leaves the padded rows of S at zero and the inner loops free of tests. The
+// tokens' vectors come through a two-stage cp.async ring, REC_TS tokens a stage, so the next tokens arrive while
+// these are worked on; a thread's rows are 4 P apart in fours, so it reads them 16 bytes at a time and the lanes of
+// a column read neighbouring 16 bytes.
 constexpr int MODE_DECAY = 0, MODE_SSM = 1, MODE_DELTA = 2;
 constexpr int REC_RPT = 16;
-constexpr int REC_WARPS = 4;
-constexpr int REC_THREADS = REC_WARPS * 32;
+constexpr int REC_THREADS = 128;
+constexpr int REC_TS = 16;
 
 struct RecArgs {
   const void* q; const void* k; const void* v;      // [T, *] activations: row strides below, head h at h * dk (dv)
@@ -107,167 +161,251 @@ struct RecArgs {
   float* state;                                      // [slots, H, dk, dv]
   const int* slots; const int* cu_q;
   float* out; int out_stride;                        // [T, H * dv] float
-  int H, Hqk, dk, dv, P, ts;
+  int H, Hqk, dk, dv, P, dkp, dvp, n_tokens;
   float q_scale;
+  // float work space, made by the first kernel: qf, kf [T, Hqk, dkp]; af [T, H, dkp] (DELTA); vf [T, H, dvp]; sc, dec [T, H]
+  float *qf, *kf, *af, *vf, *sc, *dec;
 };
 
+// grid (tokens, max(H, Hqk)); 128 threads.
 template <typename T, int MODE>
-__global__ void __launch_bounds__(REC_THREADS) recurrence_kernel(RecArgs a) {
-  extern __shared__ float smem[];
-  const int dk = a.dk, dv = a.dv, P = a.P, TS = a.ts;
-  const int VC = REC_THREADS / P;                       // columns of this block
-  float* qs = smem;                                     // [TS][dk]
-  float* ks = qs + TS * dk;                             // [TS][dk]
-  float* vs = ks + TS * dk;                             // [TS][VC]
-  float* as = vs + TS * VC;                             // [TS][dk] (DELTA) or [TS] (SSM)
-  float* bs = as + (MODE == MODE_DELTA ? TS * dk : TS); // [TS] beta (DELTA) or dt (SSM)
+__global__ void __launch_bounds__(REC_THREADS) recurrence_prep_kernel(RecArgs a) {
+  __shared__ float red[32];
+  const int t = blockIdx.x, h = blockIdx.y, tid = threadIdx.x;
+  const int dk = a.dk, dkp = a.dkp, dv = a.dv, dvp = a.dvp;
+  if (h < a.Hqk) {
+    const T* qr = (const T*)a.q + (size_t)t * a.q_stride + (size_t)h * dk;
+    const T* kr = (const T*)a.k + (size_t)t * a.k_stride + (size_t)h * dk;
+    float* qo = a.qf + ((size_t)t * a.Hqk + h) * dkp;
+    float* ko = a.kf + ((size_t)t * a.Hqk + h) * dkp;
+    float fq = 1.f, fk = 1.f;
+    if (MODE == MODE_DELTA) {
+      float sq = 0.f, sk = 0.f;
+      for (int i = tid; i < dk; i += REC_THREADS) {
+        const float x = to_float(qr[i]), y = to_float(kr[i]);
+        sq += x * x;
+        sk += y * y;
+      }
+      sq = block_sum(sq, red);
+      sk = block_sum(sk, red);
+      fq = a.q_scale / sqrtf(sq + 1e-6f);
+      fk = 1.f / sqrtf(sk + 1e-6f);
+    }
+    for (int i = tid; i < dkp; i += REC_THREADS) {
+      float x = 0.f, y = 0.f;
+      if (i < dk) {
+        x = to_float(qr[i]);
+        y = to_float(kr[i]);
+        if (MODE == MODE_DECAY) { x = silu_f(x); y = silu_f(y); }
+        x *= fq;
+        y *= fk;
+      }
+      qo[i] = x;
+      ko[i] = y;
+    }
+  }
+  if (h < a.H) {
+    const T* vr = (const T*)a.v + (size_t)t * a.v_stride + (size_t)h * dv;
+    float* vo = a.vf + ((size_t)t * a.H + h) * dvp;
+    for (int j = tid; j < dvp; j += REC_THREADS) {
+      float x = j < dv ? to_float(vr[j]) : 0.f;
+      if (MODE == MODE_DECAY) x = silu_f(x);
+      vo[j] = x;
+    }
+    if (MODE == MODE_DELTA) {
+      const float neg_a = -expf(load_w(a.a_log, a.par_dtype, h));
+      const T* rr = (const T*)a.rate + (size_t)t * a.rate_stride + (size_t)h * dk;
+      float* ao = a.af + ((size_t)t * a.H + h) * dkp;
+      for (int i = tid; i < dkp; i += REC_THREADS)
+        ao[i] = i < dk ? expf(neg_a * softplus_f(to_float(rr[i]) + load_w(a.dt_bias, a.par_dtype, (size_t)h * dk + i))) : 1.f;
+    }
+    if (tid == 0) {
+      float sc = 1.f, dec = 1.f;
+      if (MODE == MODE_DECAY) dec = ((const float*)a.decay)[h];
+      if (MODE == MODE_SSM) {
+        sc = softplus_f(to_float(((const T*)a.aux)[(size_t)t * a.aux_stride + h]) + load_w(a.dt_bias, a.par_dtype, h));
+        dec = expf(-expf(load_w(a.a_log, a.par_dtype, h)) * sc);
+      }
+      if (MODE == MODE_DELTA) sc = sigmoid_f(to_float(((const T*)a.aux)[(size_t)t * a.aux_stride + h]));
+      a.sc[(size_t)t * a.H + h] = sc;
+      a.dec[(size_t)t * a.H + h] = dec;
+    }
+  }
+}
+
+__device__ __forceinline__ void rec_cp16(float* smem, const float* g) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((unsigned)__cvta_generic_to_shared(smem)), "l"(g));
+}
+__device__ __forceinline__ void rec_cp4(float* smem, const float* g) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"((unsigned)__cvta_generic_to_shared(smem)), "l"(g));
+}
+
+// grid (dvp / VC, H, rows); 128 threads; VC = 128 / P columns a block.
+template <bool DELTA, bool SKIP>
+__global__ void __launch_bounds__(REC_THREADS) recurrence_scan_kernel(RecArgs a) {
+  extern __shared__ __align__(16) float smem[];
+  const int dk = a.dk, dv = a.dv, P = a.P, dkp = a.dkp, dvp = a.dvp, H = a.H;
+  const int VC = REC_THREADS / P;
+  const int per_tok = (DELTA ? 3 : 2) * dkp + VC;                    // floats of a token's vectors in a stage
+  const int stage_floats = REC_TS * per_tok + 2 * REC_TS;             // + sc, dec
   const int r = blockIdx.z, h = blockIdx.y, j0 = blockIdx.x * VC;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int part = lane % P, col = warp * (32 / P) + lane / P;
   const int j = j0 + col;
   const bool col_ok = j < dv;
   const int q0 = a.cu_q[r], n = a.cu_q[r + 1] - q0;
-  const int hq = h / (a.H / a.Hqk);                     // the q/k head (or group) this head reads
-  float* S = a.state + (((size_t)a.slots[r] * a.H + h) * dk) * dv;
+  const int hq = h / (H / a.Hqk);
+  float* S = a.state + (((size_t)a.slots[r] * H + h) * dk) * dv;
   float s[REC_RPT];
 #pragma unroll
-  for (int u = 0; u < REC_RPT; ++u) {
-    const int i = part + P * u;
-    s[u] = (col_ok && i < dk) ? S[(size_t)i * dv + j] : 0.f;
+  for (int x = 0; x < REC_RPT; ++x) {
+    const int i = (x >> 2) * 4 * P + part * 4 + (x & 3);
+    s[x] = (col_ok && i < dk) ? S[(size_t)i * dv + j] : 0.f;
   }
-  const T* qp = (const T*)a.q; const T* kp = (const T*)a.k; const T* vp = (const T*)a.v;
-  float head_decay = 1.f, neg_a = 0.f, dt_b = 0.f, d_skip = 0.f;
-  if (MODE == MODE_DECAY) head_decay = ((const float*)a.decay)[h];
-  if (MODE == MODE_SSM) {
-    neg_a = -expf(load_w(a.a_log, a.par_dtype, h));
-    dt_b = load_w(a.dt_bias, a.par_dtype, h);
-    d_skip = load_w(a.d_skip, a.par_dtype, h);
-  }
-  if (MODE == MODE_DELTA) neg_a = -expf(load_w(a.a_log, a.par_dtype, h));
+  float d_skip = 0.f;
+  if (SKIP) d_skip = load_w(a.d_skip, a.par_dtype, h);
 
-  for (int t0 = 0; t0 < n; t0 += TS) {
-    const int nt = min(TS, n - t0);
-    __syncthreads();                                    // the chunk before has been consumed
-    for (int w = tid; w < nt * dk; w += REC_THREADS) {
-      const int tt = w / dk, i = w - tt * dk;
-      const size_t row = (size_t)(q0 + t0 + tt);
-      float qv = to_float(qp[row * a.q_stride + (size_t)hq * dk + i]);
-      float kv = to_float(kp[row * a.k_stride + (size_t)hq * dk + i]);
-      if (MODE == MODE_DECAY) { qv = silu_f(qv); kv = silu_f(kv); }
-      qs[w] = qv;
-      ks[w] = kv;
-      if (MODE == MODE_DELTA) {
-        const float rate = to_float(((const T*)a.rate)[row * a.rate_stride + (size_t)h * dk + i]) +
-                           load_w(a.dt_bias, a.par_dtype, (size_t)h * dk + i);
-        as[w] = expf(neg_a * softplus_f(rate));
-      }
+  auto fetch = [&](int stage, int t0) {
+    float* base = smem + (size_t)stage * stage_floats;
+    const int nt = min(REC_TS, n - t0);
+    const int row16 = dkp / 4;                                        // 16-byte pieces of a q (k, a) row
+    for (int w = tid; w < nt * row16; w += REC_THREADS) {
+      const int tt = w / row16, c = (w - tt * row16) * 4;
+      const size_t tok = (size_t)(q0 + t0 + tt);
+      float* dst = base + (size_t)tt * per_tok;
+      rec_cp16(dst + c, a.qf + (tok * a.Hqk + hq) * dkp + c);
+      rec_cp16(dst + dkp + c, a.kf + (tok * a.Hqk + hq) * dkp + c);
+      if (DELTA) rec_cp16(dst + 2 * dkp + c, a.af + (tok * H + h) * dkp + c);
     }
-    for (int w = tid; w < nt * VC; w += REC_THREADS) {
-      const int tt = w / VC, c = w - tt * VC;
-      float vv = 0.f;
-      if (j0 + c < dv) vv = to_float(vp[(size_t)(q0 + t0 + tt) * a.v_stride + (size_t)h * dv + j0 + c]);
-      if (MODE == MODE_DECAY) vv = silu_f(vv);
-      vs[w] = vv;
+    const int v16 = VC / 4;
+    for (int w = tid; w < nt * v16; w += REC_THREADS) {
+      const int tt = w / v16, c = (w - tt * v16) * 4;
+      rec_cp16(base + (size_t)tt * per_tok + (DELTA ? 3 : 2) * dkp + c, a.vf + ((size_t)(q0 + t0 + tt) * H + h) * dvp + j0 + c);
     }
-    if (MODE != MODE_DECAY) {
-      for (int tt = tid; tt < nt; tt += REC_THREADS) {
-        const float raw = to_float(((const T*)a.aux)[(size_t)(q0 + t0 + tt) * a.aux_stride + h]);
-        if (MODE == MODE_SSM) {
-          const float dt = softplus_f(raw + dt_b);
-          bs[tt] = dt;
-          as[tt] = expf(neg_a * dt);
-        } else {
-          bs[tt] = sigmoid_f(raw);
-        }
-      }
+    for (int w = tid; w < 2 * nt; w += REC_THREADS) {
+      const int tt = w >> 1;
+      rec_cp4(base + REC_TS * per_tok + w, ((w & 1) ? a.dec : a.sc) + (size_t)(q0 + t0 + tt) * H + h);
     }
-    __syncthreads();
-    if (MODE == MODE_DELTA) {
-      // queries and keys become unit vectors (the query also times q_scale): a warp per token and vector
-      for (int w = warp; w < 2 * nt; w += REC_WARPS) {
-        float* vec = (w < nt ? qs : ks) + (size_t)(w < nt ? w : w - nt) * dk;
-        float ss = 0.f;
-        for (int i = lane; i < dk; i += 32) ss += vec[i] * vec[i];
-        ss = warp_sum(ss);
-        const float f = (w < nt ? a.q_scale : 1.f) / sqrtf(ss + 1e-6f);
-        for (int i = lane; i < dk; i += 32) vec[i] *= f;
-      }
-      __syncthreads();
-    }
+  };
+
+  if (n > 0) fetch(0, 0);
+  asm volatile("cp.async.commit_group;");
+  int stage = 0;
+  for (int t0 = 0; t0 < n; t0 += REC_TS, stage ^= 1) {
+    if (t0 + REC_TS < n) fetch(stage ^ 1, t0 + REC_TS);
+    asm volatile("cp.async.commit_group;");
+    asm volatile("cp.async.wait_group 1;");
+    __syncthreads();                                                  // this stage has arrived for every thread
+    const float* base = smem + (size_t)stage * stage_floats;
+    const int nt = min(REC_TS, n - t0);
     for (int tt = 0; tt < nt; ++tt) {
-      const float* qt = qs + tt * dk;
-      const float* kt = ks + tt * dk;
-      const float vv = vs[tt * VC + col];
-      float dec = head_decay, u = vv;
-      if (MODE == MODE_SSM) { dec = as[tt]; u = bs[tt] * vv; }
-      if (MODE == MODE_DELTA) {
-        float dot = 0.f;
+      const float4* q4 = reinterpret_cast<const float4*>(base + (size_t)tt * per_tok);
+      const float4* k4 = q4 + dkp / 4;
+      const float4* a4 = k4 + dkp / 4;
+      const float vv = base[(size_t)tt * per_tok + (DELTA ? 3 : 2) * dkp + col];
+      const float sc = base[REC_TS * per_tok + 2 * tt], dec = base[REC_TS * per_tok + 2 * tt + 1];
+      float4 kk[4], qq[4];
 #pragma unroll
-        for (int x = 0; x < REC_RPT; ++x) {
-          const int i = part + P * x;
-          if (i < dk) {
-            s[x] *= as[tt * dk + i];
-            dot += s[x] * kt[i];
-          }
-        }
-        for (int o = P >> 1; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
-        u = bs[tt] * (vv - dot);
+      for (int x4 = 0; x4 < 4; ++x4) {
+        kk[x4] = k4[x4 * P + part];
+        qq[x4] = q4[x4 * P + part];
       }
-      float o_acc = 0.f;
+      float u;
+      if (DELTA) {
+        float dot[4];
 #pragma unroll
-      for (int x = 0; x < REC_RPT; ++x) {
-        const int i = part + P * x;
-        if (i < dk) {
-          if (MODE != MODE_DELTA) s[x] *= dec;
-          s[x] += kt[i] * u;
-          o_acc += s[x] * qt[i];
+        for (int x4 = 0; x4 < 4; ++x4) {
+          const float4 aa = a4[x4 * P + part];
+          s[4 * x4] *= aa.x; s[4 * x4 + 1] *= aa.y; s[4 * x4 + 2] *= aa.z; s[4 * x4 + 3] *= aa.w;
+          dot[x4] = s[4 * x4] * kk[x4].x + s[4 * x4 + 1] * kk[x4].y + s[4 * x4 + 2] * kk[x4].z + s[4 * x4 + 3] * kk[x4].w;
         }
+        float d = (dot[0] + dot[1]) + (dot[2] + dot[3]);
+        for (int o = P >> 1; o > 0; o >>= 1) d += __shfl_xor_sync(0xffffffffu, d, o);
+        u = sc * (vv - d);
+      } else {
+#pragma unroll
+        for (int x = 0; x < REC_RPT; ++x) s[x] *= dec;
+        u = sc * vv;
       }
+      float oo[4];
+#pragma unroll
+      for (int x4 = 0; x4 < 4; ++x4) {
+        s[4 * x4] += kk[x4].x * u; s[4 * x4 + 1] += kk[x4].y * u; s[4 * x4 + 2] += kk[x4].z * u; s[4 * x4 + 3] += kk[x4].w * u;
+        oo[x4] = s[4 * x4] * qq[x4].x + s[4 * x4 + 1] * qq[x4].y + s[4 * x4 + 2] * qq[x4].z + s[4 * x4 + 3] * qq[x4].w;
+      }
+      float o_acc = (oo[0] + oo[1]) + (oo[2] + oo[3]);
       for (int o = P >> 1; o > 0; o >>= 1) o_acc += __shfl_xor_sync(0xffffffffu, o_acc, o);
-      if (MODE == MODE_SSM) o_acc += d_skip * vv;
+      if (SKIP) o_acc += d_skip * vv;
       if (part == 0 && col_ok) a.out[(size_t)(q0 + t0 + tt) * a.out_stride + (size_t)h * dv + j] = o_acc;
     }
+    __syncthreads();                                                  // before the stage after next overwrites this one
   }
+  asm volatile("cp.async.wait_group 0;");
 #pragma unroll
-  for (int u = 0; u < REC_RPT; ++u) {
-    const int i = part + P * u;
-    if (col_ok && i < dk) S[(size_t)i * dv + j] = s[u];
+  for (int x = 0; x < REC_RPT; ++x) {
+    const int i = (x >> 2) * 4 * P + part * 4 + (x & 3);
+    if (col_ok && i < dk) S[(size_t)i * dv + j] = s[x];
   }
 }
 
-template <typename T, int MODE>
-int launch_recurrence(RecArgs a, int n_rows, cudaStream_t stream) {
+static inline int rec_lanes(int dk) {
   int P = 1;
-  while (P * REC_RPT < a.dk) P <<= 1;
+  while (P * REC_RPT < dk) P <<= 1;
+  return P;
+}
+
+static inline long long rec_work_floats(int mode, int n_tokens, int H, int Hqk, int dk, int dv) {
+  const int P = rec_lanes(dk), dkp = P * REC_RPT, VC = REC_THREADS / P, dvp = (dv + VC - 1) / VC * VC;
+  return (long long)n_tokens * ((long long)2 * Hqk * dkp + (mode == MODE_DELTA ? (long long)H * dkp : 0) + (long long)H * dvp + 2 * H) + 16;
+}
+
+template <typename T, int MODE>
+int launch_recurrence(RecArgs a, float* work, int n_rows, cudaStream_t stream) {
+  const int P = rec_lanes(a.dk);
   if (P > 32) return SB_ERR_LIMIT;
   a.P = P;
+  a.dkp = P * REC_RPT;
   const int VC = REC_THREADS / P;
-  const int per_token = 2 * a.dk + VC + (MODE == MODE_DELTA ? a.dk : 1) + 1;
-  int ts = (40 * 1024 / 4) / per_token;
-  if (ts > 16) ts = 16;
-  if (ts < 1) return SB_ERR_LIMIT;
-  a.ts = ts;
-  const size_t smem = (size_t)ts * per_token * sizeof(float);
-  dim3 grid((a.dv + VC - 1) / VC, a.H, n_rows);
-  recurrence_kernel<T, MODE><<<grid, REC_THREADS, smem, stream>>>(a);
+  a.dvp = (a.dv + VC - 1) / VC * VC;
+  const size_t T_ = (size_t)a.n_tokens;
+  a.qf = work;
+  a.kf = a.qf + T_ * a.Hqk * a.dkp;
+  a.af = a.kf + T_ * a.Hqk * a.dkp;
+  a.vf = a.af + (MODE == MODE_DELTA ? T_ * a.H * a.dkp : 0);
+  a.sc = a.vf + T_ * a.H * a.dvp;
+  a.dec = a.sc + T_ * a.H;
+  if (a.n_tokens > 0x7fffffff / 1 || a.H > 65535 || a.Hqk > 65535) return SB_ERR_LIMIT;
+  recurrence_prep_kernel<T, MODE><<<dim3(a.n_tokens, a.H > a.Hqk ? a.H : a.Hqk), REC_THREADS, 0, stream>>>(a);
+  SB_LAUNCH_CHECK();
+  const int per_tok = (MODE == MODE_DELTA ? 3 : 2) * a.dkp + VC;
+  const size_t smem = (size_t)2 * (REC_TS * per_tok + 2 * REC_TS) * sizeof(float);
+  dim3 grid(a.dvp / VC, a.H, n_rows);
+  auto kernel = recurrence_scan_kernel<MODE == MODE_DELTA, MODE == MODE_SSM>;
+  if (smem > 48 * 1024) {
+    if (smem > 200 * 1024) return SB_ERR_LIMIT;
+    cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  }
+  kernel<<<grid, REC_THREADS, smem, stream>>>(a);
   return (int)cudaGetLastError();
 }
 
 // ------------------------------------------------------------------------------------------ norm and gate
-// out[t, c] = scale * post( rms_g( pre(y[t, c]) ) * w[c mod w_size] ), a warp per (token, group):
+// out[t, c] = scale * post( rms_g( pre(y[t, c]) ) * w[c mod w_size] ), a warp per (token, group), or the whole block of 128
+// threads for a group of more than 512 values (TPG threads a group):
 // (y is float, or of the activations' type)
 //   pre:  times act(gate[t, c']) if the gate comes first; rms_g: divided by the root mean square of the group's
 //   values (+ eps inside the root; no division with groups == 0, where a group is just a warp's share of the row);
 //   post: times act(gate[t, c']) if the gate comes last. c' = c, or c / (C / gate_cols) for a gate per head.
-template <typename T>
+template <typename T, int TPG>
 __global__ void __launch_bounds__(128) gated_norm_kernel(const void* __restrict__ y, int y_dtype, int y_stride, const T* __restrict__ gate,
                                                          int gate_stride, int gate_cols, int gate_act, int gate_first,
                                                          const void* __restrict__ weight, int w_dtype, int w_size, T* __restrict__ out,
                                                          int out_stride, int n_tokens, int C, int groups, int normalise, float eps,
                                                          float scale) {
-  const int lane = threadIdx.x & 31;
-  const long long wid = (long long)blockIdx.x * 4 + (threadIdx.x >> 5);
-  if (wid >= (long long)n_tokens * groups) return;
+  __shared__ float red[32];
+  const int lane = TPG == 32 ? (threadIdx.x & 31) : threadIdx.x;
+  const long long wid = TPG == 32 ? (long long)blockIdx.x * 4 + (threadIdx.x >> 5) : (long long)blockIdx.x;
+  if (wid >= (long long)n_tokens * groups) return;      // (a whole warp, or the whole block, leaves together)
   const int t = (int)(wid / groups), g = (int)(wid - (long long)t * groups);
   const int gs = C / groups, c0 = g * gs;
   const int per_gate = gate ? C / gate_cols : 1;
@@ -280,15 +418,15 @@ __global__ void __launch_bounds__(128) gated_norm_kernel(const void* __restrict_
   float inv = 1.f;
   if (normalise) {
     float ss = 0.f;
-    for (int c = c0 + lane; c < c0 + gs; c += 32) {
+    for (int c = c0 + lane; c < c0 + gs; c += TPG) {
       float v = load_w(y, y_dtype, yr + c);
       if (gr && gate_first) v *= gate_of(c);
       ss += v * v;
     }
-    ss = warp_sum(ss);
+    ss = TPG == 32 ? warp_sum(ss) : block_sum(ss, red);
     inv = 1.f / sqrtf(ss / (float)gs + eps);
   }
-  for (int c = c0 + lane; c < c0 + gs; c += 32) {
+  for (int c = c0 + lane; c < c0 + gs; c += TPG) {
     float v = load_w(y, y_dtype, yr + c);
     if (gr && gate_first) v *= gate_of(c);
     v *= inv;
@@ -359,8 +497,14 @@ SB_EXPORT int sb_causal_conv(const void* x, int x_stride, const void* w, const v
       conv_state_kernel<float><<<sgrid, CONV_THREADS, 0, stream>>>((const float*)x, x_stride, state, slots, cu_q, C, taps);
   } else if (dtype == SB_DTYPE_BF16) {
     typedef __nv_bfloat16 B;
-    causal_conv_kernel<B><<<grid, CONV_THREADS, 0, stream>>>((const B*)x, x_stride, (const B*)w, (const B*)bias, state, slots, cu_q,
-                                                              token_row, (B*)out, out_stride, C, taps, act, residual, pure_decode);
+    const bool by8 = C % 8 == 0 && x_stride % 8 == 0 && out_stride % 8 == 0 && aligned16(x) && aligned16(out) && (!state || aligned16(state));
+    if (by8)
+      causal_conv8_kernel<<<dim3((C / 8 + CONV_THREADS - 1) / CONV_THREADS, n_tokens), CONV_THREADS, 0, stream>>>(
+          (const B*)x, x_stride, (const B*)w, (const B*)bias, state, slots, cu_q, token_row, (B*)out, out_stride, C, taps, act, residual,
+          pure_decode);
+    else
+      causal_conv_kernel<B><<<grid, CONV_THREADS, 0, stream>>>((const B*)x, x_stride, (const B*)w, (const B*)bias, state, slots, cu_q,
+                                                                token_row, (B*)out, out_stride, C, taps, act, residual, pure_decode);
     SB_LAUNCH_CHECK();
     if (!pure_decode && taps > 1)
       conv_state_kernel<B><<<sgrid, CONV_THREADS, 0, stream>>>((const B*)x, x_stride, state, slots, cu_q, C, taps);
@@ -371,29 +515,38 @@ SB_EXPORT int sb_causal_conv(const void* x, int x_stride, const void* w, const v
   return 0;
 }
 
+// Floats of work space sb_linear_recurrence needs for a step of n_tokens tokens.
+SB_EXPORT long long sb_linear_recurrence_work_floats(int mode, int n_tokens, int H, int Hqk, int dk, int dv) {
+  if (dk <= 0 || dk > 32 * REC_RPT) return -1;
+  return rec_work_floats(mode, n_tokens, H, Hqk, dk, dv);
+}
+
 // The three recurrences (mode 0: fixed decay per head with silu on q, k, v; 1: selective state space; 2: gated delta
-// rule). See RecArgs for what each pointer is; unused ones are null. out is float [T, H * dv].
+// rule). See RecArgs for what each pointer is; unused ones are null. out is float [T, H * dv]; work: 16-byte aligned floats,
+// as many as sb_linear_recurrence_work_floats says.
 SB_EXPORT int sb_linear_recurrence(int mode, const void* q, int q_stride, const void* k, int k_stride, const void* v, int v_stride,
                                    const void* aux, int aux_stride, const void* rate, int rate_stride, const float* decay,
                                    const void* a_log, const void* dt_bias, const void* d_skip, int par_dtype, float* state,
                                    const int* slots, const int* cu_q, float* out, int out_stride, int H, int Hqk, int dk, int dv,
-                                   float q_scale, int n_rows, int dtype, cudaStream_t stream) {
-  if (n_rows <= 0) return 0;
+                                   float q_scale, int n_rows, int n_tokens, float* work, int dtype, cudaStream_t stream) {
+  if (n_rows <= 0 || n_tokens <= 0) return 0;
+  if (!work || !aligned16(work)) return SB_ERR_ALIGN;
   if (H <= 0 || Hqk <= 0 || H % Hqk || dk <= 0 || dv <= 0) return SB_ERR_SHAPE;
   if (n_rows > 65535 || H > 65535 || dk > 32 * REC_RPT) return SB_ERR_LIMIT;
   RecArgs a;
   a.q = q; a.k = k; a.v = v; a.q_stride = q_stride; a.k_stride = k_stride; a.v_stride = v_stride;
   a.aux = aux; a.aux_stride = aux_stride; a.rate = rate; a.rate_stride = rate_stride; a.decay = decay;
   a.a_log = a_log; a.dt_bias = dt_bias; a.d_skip = d_skip; a.par_dtype = par_dtype; a.state = state; a.slots = slots; a.cu_q = cu_q;
-  a.out = out; a.out_stride = out_stride; a.H = H; a.Hqk = Hqk; a.dk = dk; a.dv = dv; a.P = 1; a.ts = 1; a.q_scale = q_scale;
+  a.out = out; a.out_stride = out_stride; a.H = H; a.Hqk = Hqk; a.dk = dk; a.dv = dv; a.P = 1; a.dkp = a.dvp = 0; a.n_tokens = n_tokens;
+  a.q_scale = q_scale; a.qf = a.kf = a.af = a.vf = a.sc = a.dec = nullptr;
   if (dtype == SB_DTYPE_F32) {
-    if (mode == MODE_DECAY) return launch_recurrence<float, MODE_DECAY>(a, n_rows, stream);
-    if (mode == MODE_SSM) return launch_recurrence<float, MODE_SSM>(a, n_rows, stream);
-    if (mode == MODE_DELTA) return launch_recurrence<float, MODE_DELTA>(a, n_rows, stream);
+    if (mode == MODE_DECAY) return launch_recurrence<float, MODE_DECAY>(a, work, n_rows, stream);
+    if (mode == MODE_SSM) return launch_recurrence<float, MODE_SSM>(a, work, n_rows, stream);
+    if (mode == MODE_DELTA) return launch_recurrence<float, MODE_DELTA>(a, work, n_rows, stream);
   } else if (dtype == SB_DTYPE_BF16) {
-    if (mode == MODE_DECAY) return launch_recurrence<__nv_bfloat16, MODE_DECAY>(a, n_rows, stream);
-    if (mode == MODE_SSM) return launch_recurrence<__nv_bfloat16, MODE_SSM>(a, n_rows, stream);
-    if (mode == MODE_DELTA) return launch_recurrence<__nv_bfloat16, MODE_DELTA>(a, n_rows, stream);
+    if (mode == MODE_DECAY) return launch_recurrence<__nv_bfloat16, MODE_DECAY>(a, work, n_rows, stream);
+    if (mode == MODE_SSM) return launch_recurrence<__nv_bfloat16, MODE_SSM>(a, work, n_rows, stream);
+    if (mode == MODE_DELTA) return launch_recurrence<__nv_bfloat16, MODE_DELTA>(a, work, n_rows, stream);
   } else {
     return SB_ERR_DTYPE;
   }
@@ -410,14 +563,29 @@ SB_EXPORT int sb_gated_norm(const void* y, int y_dtype, int y_stride, const void
   if (groups <= 0) groups = gate ? gate_cols : 1;
   if (C % groups || (gate && (gate_cols <= 0 || C % gate_cols)) || (weight && (w_size <= 0 || C % w_size))) return SB_ERR_SHAPE;
   const long long warps = (long long)n_tokens * groups;
-  const long long blocks = (warps + 3) / 4;
+  const bool wide = C / groups > 512;                     // a block per group
+  const long long blocks = wide ? warps : (warps + 3) / 4;
   if (blocks > 0x7fffffffLL) return SB_ERR_LIMIT;
+  if (wide) {
+    if (dtype == SB_DTYPE_F32)
+      gated_norm_kernel<float, 128><<<(unsigned)blocks, 128, 0, stream>>>(y, y_dtype, y_stride, (const float*)gate, gate_stride, gate_cols,
+                                                                           gate_act, gate_first, weight, w_dtype, w_size, (float*)out,
+                                                                           out_stride, n_tokens, C, groups, normalise, eps, scale);
+    else if (dtype == SB_DTYPE_BF16)
+      gated_norm_kernel<__nv_bfloat16, 128><<<(unsigned)blocks, 128, 0, stream>>>(
+          y, y_dtype, y_stride, (const __nv_bfloat16*)gate, gate_stride, gate_cols, gate_act, gate_first, weight, w_dtype, w_size,
+          (__nv_bfloat16*)out, out_stride, n_tokens, C, groups, normalise, eps, scale);
+    else
+      return SB_ERR_DTYPE;
+    SB_LAUNCH_CHECK();
+    return 0;
+  }
   if (dtype == SB_DTYPE_F32)
-    gated_norm_kernel<float><<<(unsigned)blocks, 128, 0, stream>>>(y, y_dtype, y_stride, (const float*)gate, gate_stride, gate_cols, gate_act,
+    gated_norm_kernel<float, 32><<<(unsigned)blocks, 128, 0, stream>>>(y, y_dtype, y_stride, (const float*)gate, gate_stride, gate_cols, gate_act,
                                                                     gate_first, weight, w_dtype, w_size, (float*)out, out_stride, n_tokens,
                                                                     C, groups, normalise, eps, scale);
   else if (dtype == SB_DTYPE_BF16)
-    gated_norm_kernel<__nv_bfloat16><<<(unsigned)blocks, 128, 0, stream>>>(y, y_dtype, y_stride, (const __nv_bfloat16*)gate, gate_stride, gate_cols,
+    gated_norm_kernel<__nv_bfloat16, 32><<<(unsigned)blocks, 128, 0, stream>>>(y, y_dtype, y_stride, (const __nv_bfloat16*)gate, gate_stride, gate_cols,
                                                                             gate_act, gate_first, weight, w_dtype, w_size,
                                                                             (__nv_bfloat16*)out, out_stride, n_tokens, C, groups, normalise,
                                                                             eps, scale);

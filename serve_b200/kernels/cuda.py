@@ -633,12 +633,20 @@ class CudaKernels:
         softplus(aux + dt_bias), o += d_skip v; "delta": S = g S, S += k (beta (v - S^T k))^T with g = exp(-exp(a_log)
         softplus(rate + dt_bias)), beta = sigmoid(aux), q and k made unit vectors. out: float [T, heads * dv]."""
         par = a_log if a_log is not None else None
-        self.launches += 1
-        _check(self._seq_lib().sb_linear_recurrence(
-            {"decay": 0, "ssm": 1, "delta": 2}[mode], _p(q), q.stride(0), _p(k), k.stride(0), _p(v), v.stride(0),
+        lib = self._seq_lib()
+        code = {"decay": 0, "ssm": 1, "delta": 2}[mode]
+        lib.sb_linear_recurrence_work_floats.restype = ctypes.c_longlong
+        need = lib.sb_linear_recurrence_work_floats(code, q.shape[0], heads, qk_heads, dk, dv)
+        if need < 0:
+            raise KernelError(f"linear recurrence: a state of {dk} rows is beyond the kernel's 512")
+        work = torch.empty(need, dtype=torch.float32, device=q.device)       # what the first kernel leaves for the second
+        self.launches += 2
+        _check(lib.sb_linear_recurrence(
+            code, _p(q), q.stride(0), _p(k), k.stride(0), _p(v), v.stride(0),
             _p(aux), aux.stride(0) if aux is not None else 0, _p(rate), rate.stride(0) if rate is not None else 0, _p(decay),
             _p(a_log), _p(dt_bias), _p(d_skip), _DT[par.dtype] if par is not None else 0, _p(state), _p(ctx.slots), _p(ctx.cu_q),
-            _p(out), out.stride(0), heads, qk_heads, dk, dv, ctypes.c_float(q_scale), ctx.shape.rows, _DT[v.dtype], self._s()),
+            _p(out), out.stride(0), heads, qk_heads, dk, dv, ctypes.c_float(q_scale), ctx.shape.rows, q.shape[0], _p(work),
+            _DT[v.dtype], self._s()),
             "linear recurrence")
 
     def gated_norm(self, y, out, groups: int = 0, eps: float = 0.0, weight=None, gate=None, gate_act: str = "sigmoid",
