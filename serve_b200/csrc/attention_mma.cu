@@ -71,6 +71,8 @@ struct Params {
   int H, Hkv, G, ps, num_pages;
   int ps_shift;     // log2(ps) if ps is a power of two, else -1: a shift in place of a division in the key loops
   float scale_log2; int window;
+  const float* slopes;   // one per query head, or null: slope * (position - key) is taken off a score (in the score's own units)
+  int chunk;             // > 0: a query sees only the keys from floor(position / chunk) * chunk on
   bf16* out;
   // deep shape only
   int split_size, num_splits;
@@ -223,11 +225,14 @@ __global__ void __launch_bounds__(THREADS, (D <= 64 ? 4 : 1)) attention_wide_ker
   const int L = p.kv_len[r];
   const int p0 = L - qn;                            // position of the request's first query
   const int tok_first = m0 / G, row_last = min(m0 + BM, M) - 1;
-  const int lo = p.window > 0 ? max(0, p0 + tok_first - p.window + 1) : 0;
+  int lo = p.window > 0 ? max(0, p0 + tok_first - p.window + 1) : 0;
+  if (p.chunk > 0) lo = max(lo, ((p0 + tok_first) / p.chunk) * p.chunk);
   const int hi = p0 + row_last / G + 1;             // exclusive, <= L
-  // keys every row of the tile may see without a mask
-  const int free_lo = p.window > 0 ? max(lo, p0 + row_last / G - p.window + 1) : lo;
-  const int free_hi = min(hi, p0 + tok_first + 1);
+  // keys every row of the tile may see without a mask (none with a distance bias or blocks of positions: every score
+  // then goes through the masked path, which also takes the bias off)
+  const bool by_distance = p.slopes != nullptr || p.chunk > 0;
+  const int free_lo = by_distance ? 0x7fffffff : (p.window > 0 ? max(lo, p0 + row_last / G - p.window + 1) : lo);
+  const int free_hi = by_distance ? 0 : min(hi, p0 + tok_first + 1);
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int g = lane >> 2, tq = lane & 3;
   const int* bt = p.block_table + (size_t)r * p.bt_width;
@@ -256,6 +261,10 @@ __global__ void __launch_bounds__(THREADS, (D <= 64 ? 4 : 1)) attention_wide_ker
 
   const int row_a = m0 + warp * 16 + g, row_b = row_a + 8;
   const int pos_a = row_a < M ? p0 + row_a / G : -1, pos_b = row_b < M ? p0 + row_b / G : -1;
+  const float slope_a = (p.slopes && row_a < M) ? p.slopes[hk * G + row_a % G] * LOG2E : 0.f;
+  const float slope_b = (p.slopes && row_b < M) ? p.slopes[hk * G + row_b % G] * LOG2E : 0.f;
+  const int first_a = (p.chunk > 0 && pos_a >= 0) ? (pos_a / p.chunk) * p.chunk : 0;
+  const int first_b = (p.chunk > 0 && pos_b >= 0) ? (pos_b / p.chunk) * p.chunk : 0;
   uint32_t qf[WQ_IN_REGS ? D / 16 : 1][4];
   float o[D / 8][4];
 #pragma unroll
@@ -315,10 +324,10 @@ __global__ void __launch_bounds__(THREADS, (D <= 64 ? 4 : 1)) attention_wide_ker
         for (int e = 0; e < 2; ++e) {
           const int key = kt + j * 8 + tq * 2 + e;
           const bool in_range = key >= lo && key < hi;
-          const bool ok_a = in_range && key <= pos_a && (p.window <= 0 || key > pos_a - p.window);
-          const bool ok_b = in_range && key <= pos_b && (p.window <= 0 || key > pos_b - p.window);
-          s[j][e] = ok_a ? s[j][e] * p.scale_log2 : -INFINITY;
-          s[j][2 + e] = ok_b ? s[j][2 + e] * p.scale_log2 : -INFINITY;
+          const bool ok_a = in_range && key <= pos_a && key >= first_a && (p.window <= 0 || key > pos_a - p.window);
+          const bool ok_b = in_range && key <= pos_b && key >= first_b && (p.window <= 0 || key > pos_b - p.window);
+          s[j][e] = ok_a ? s[j][e] * p.scale_log2 - slope_a * (float)(pos_a - key) : -INFINITY;
+          s[j][2 + e] = ok_b ? s[j][2 + e] * p.scale_log2 - slope_b * (float)(pos_b - key) : -INFINITY;
           mx_a = fmaxf(mx_a, s[j][e]);
           mx_b = fmaxf(mx_b, s[j][2 + e]);
         }
@@ -474,6 +483,7 @@ __global__ void __launch_bounds__(NWARPS * 32) attention_deep_kernel(const Param
   const int L = p.kv_len[r];
   const int p0 = L - qn;
   int lo = p.window > 0 ? max(0, p0 - p.window + 1) : 0;
+  if (p.chunk > 0) lo = max(lo, (p0 / p.chunk) * p.chunk);
   int hi = p0 + (M - 1) / G + 1;
   {
     // the request's keys are shared out evenly over the launch's splits, in units of one step of all the block's
@@ -549,9 +559,15 @@ __global__ void __launch_bounds__(NWARPS * 32) attention_deep_kernel(const Param
   }
   const int pos_a = g < M ? p0 + g / G : -1;
   const int pos_b = (UPPER && g + 8 < M) ? p0 + (g + 8) / G : -1;
-  // a sub-tile all of whose keys every row may see needs no mask: keys in [free_lo, free_hi)
-  const int free_lo = max(lo, p.window > 0 ? p0 + (M - 1) / G - p.window + 1 : 0);
-  const int free_hi = min(hi, p0 + 1);
+  const float slope_a = (p.slopes && g < M) ? p.slopes[hk * G + g % G] * LOG2E : 0.f;
+  const float slope_b = (UPPER && p.slopes && g + 8 < M) ? p.slopes[hk * G + (g + 8) % G] * LOG2E : 0.f;
+  const int first_a = (p.chunk > 0 && pos_a >= 0) ? (pos_a / p.chunk) * p.chunk : 0;
+  const int first_b = (p.chunk > 0 && pos_b >= 0) ? (pos_b / p.chunk) * p.chunk : 0;
+  // a sub-tile all of whose keys every row may see needs no mask: keys in [free_lo, free_hi) (none with a distance
+  // bias or blocks of positions: the masked path takes the bias off)
+  const bool by_distance = p.slopes != nullptr || p.chunk > 0;
+  const int free_lo = by_distance ? 0x7fffffff : max(lo, p.window > 0 ? p0 + (M - 1) / G - p.window + 1 : 0);
+  const int free_hi = by_distance ? 0 : min(hi, p0 + 1);
   float o[D / 8][4];
 #pragma unroll
   for (int i = 0; i < D / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
@@ -610,12 +626,12 @@ __global__ void __launch_bounds__(NWARPS * 32) attention_deep_kernel(const Param
         for (int e = 0; e < 2; ++e) {
           const int key = kbase + j * 8 + tq * 2 + e;
           const bool in_range = key >= lo && key < hi;
-          const bool ok_a = in_range && key <= pos_a && (p.window <= 0 || key > pos_a - p.window);
-          s[j][e] = ok_a ? s[j][e] * p.scale_log2 : -INFINITY;
+          const bool ok_a = in_range && key <= pos_a && key >= first_a && (p.window <= 0 || key > pos_a - p.window);
+          s[j][e] = ok_a ? s[j][e] * p.scale_log2 - slope_a * (float)(pos_a - key) : -INFINITY;
           mx_a = fmaxf(mx_a, s[j][e]);
           if (UPPER) {
-            const bool ok_b = in_range && key <= pos_b && (p.window <= 0 || key > pos_b - p.window);
-            s[j][2 + e] = ok_b ? s[j][2 + e] * p.scale_log2 : -INFINITY;
+            const bool ok_b = in_range && key <= pos_b && key >= first_b && (p.window <= 0 || key > pos_b - p.window);
+            s[j][2 + e] = ok_b ? s[j][2 + e] * p.scale_log2 - slope_b * (float)(pos_b - key) : -INFINITY;
             mx_b = fmaxf(mx_b, s[j][2 + e]);
           }
         }
@@ -761,10 +777,12 @@ SB_EXPORT long long sb_attention_mma_scratch_bytes(int n_rows, int Hkv, int num_
 // bit 1 launch the deep shape. ``longest``: no sequence of the step is longer (0: not known). With num_splits > 1 the deep shape needs
 // ``scratch`` (sb_attention_mma_scratch_bytes) and merges either in the block that finishes last (tickets: n_rows * Hkv
 // ints, zero before the first launch; every launch leaves them zero) or, with tickets == nullptr, in a second kernel.
-SB_EXPORT int sb_attention_mma(const void* qkv, int q_stride, const void* kc, const void* vc, const int* block_table, int bt_width,
-                               const int* cu_q, const int* kv_len, int H, int Hkv, int ps, int num_pages, float scale, int window,
-                               void* out, int n_rows, int max_q, int which, int longest, int num_splits, void* scratch,
-                               int* tickets, const int* wide_rows, int n_wide, cudaStream_t stream) {
+// ``slopes`` (float [H] or null) and ``chunk`` (0: none): scores that depend on distance, see Params.
+SB_EXPORT int sb_attention_mma_biased(const void* qkv, int q_stride, const void* kc, const void* vc, const int* block_table, int bt_width,
+                                      const int* cu_q, const int* kv_len, int H, int Hkv, int ps, int num_pages, float scale, int window,
+                                      void* out, int n_rows, int max_q, int which, int longest, int num_splits, void* scratch,
+                                      int* tickets, const int* wide_rows, int n_wide, const float* slopes, int chunk,
+                                      cudaStream_t stream) {
   if (n_rows <= 0 || max_q <= 0) return 0;
   if (H <= 0 || Hkv <= 0 || H % Hkv || ps <= 0 || bt_width <= 0) return SB_ERR_SHAPE;
   if (Hkv > 65535 || n_rows > 65535) return SB_ERR_LIMIT;
@@ -774,7 +792,7 @@ SB_EXPORT int sb_attention_mma(const void* qkv, int q_stride, const void* kc, co
   p.block_table = block_table; p.bt_width = bt_width; p.cu_q = cu_q; p.kv_len = kv_len;
   p.H = H; p.Hkv = Hkv; p.G = H / Hkv; p.ps = ps; p.num_pages = num_pages;
   p.ps_shift = (ps & (ps - 1)) == 0 ? __builtin_ctz((unsigned)ps) : -1;
-  p.scale_log2 = scale * LOG2E; p.window = window; p.out = (bf16*)out;
+  p.scale_log2 = scale * LOG2E; p.window = window; p.out = (bf16*)out; p.slopes = slopes; p.chunk = chunk;
   p.split_size = 0; p.num_splits = num_splits; p.part_o = nullptr; p.part_ml = nullptr; p.tickets = nullptr;
   p.wide_rows = wide_rows; p.heads_in_x = 0;
   if (which & 1) {
@@ -861,6 +879,14 @@ constexpr int kNoallocMaxDevices = 64;
 void* g_noalloc_addr[kNoallocMaxDevices];
 }  // namespace
 
+SB_EXPORT int sb_attention_mma(const void* qkv, int q_stride, const void* kc, const void* vc, const int* block_table, int bt_width,
+                               const int* cu_q, const int* kv_len, int H, int Hkv, int ps, int num_pages, float scale, int window,
+                               void* out, int n_rows, int max_q, int which, int longest, int num_splits, void* scratch,
+                               int* tickets, const int* wide_rows, int n_wide, cudaStream_t stream) {
+  return sb_attention_mma_biased(qkv, q_stride, kc, vc, block_table, bt_width, cu_q, kv_len, H, Hkv, ps, num_pages, scale, window, out,
+                                 n_rows, max_q, which, longest, num_splits, scratch, tickets, wide_rows, n_wide, nullptr, 0, stream);
+}
+
 SB_EXPORT int sb_attention_decode_noalloc_max_tiles(void) { return SB_NOALLOC_MAX_TILES; }
 
 SB_EXPORT int sb_attention_decode_noalloc(const void* qkv, int q_stride, const void* kc, const void* vc, const int* block_table,
@@ -895,7 +921,7 @@ SB_EXPORT int sb_attention_decode_noalloc(const void* qkv, int q_stride, const v
   p.block_table = block_table; p.bt_width = bt_width; p.cu_q = cu_q; p.kv_len = kv_len;
   p.H = H; p.Hkv = Hkv; p.G = G; p.ps = ps; p.num_pages = num_pages;
   p.ps_shift = (ps & (ps - 1)) == 0 ? __builtin_ctz((unsigned)ps) : -1;
-  p.scale_log2 = scale * LOG2E; p.window = window; p.out = (bf16*)out;
+  p.scale_log2 = scale * LOG2E; p.window = window; p.out = (bf16*)out; p.slopes = nullptr; p.chunk = 0;
   p.split_size = 0; p.num_splits = num_splits; p.part_o = nullptr; p.part_ml = nullptr; p.tickets = nullptr;
   p.wide_rows = nullptr;
   if (num_splits > 1) {

@@ -58,6 +58,7 @@ __global__ void __launch_bounds__(CONV_THREADS) causal_conv_kernel(
 
 // The same for eight neighbouring channels a thread, fetched 16 bytes at a time (bfloat16 with every row start and the
 // channel count a multiple of eight); the arithmetic per channel is the one above, in the same order.
+template <int TAPS>      // the number of taps when it is 2, 3 or 4 (the eight filters are then fetched 16 bytes at a time); 0: any
 __global__ void __launch_bounds__(CONV_THREADS) causal_conv8_kernel(
     const __nv_bfloat16* __restrict__ x, int x_stride, const __nv_bfloat16* __restrict__ w, const __nv_bfloat16* __restrict__ bias,
     float* __restrict__ state, const int* __restrict__ slots, const int* __restrict__ cu_q, const int* __restrict__ token_row,
@@ -67,12 +68,20 @@ __global__ void __launch_bounds__(CONV_THREADS) causal_conv8_kernel(
   if (c >= C) return;
   const int r = token_row[t];
   const int i = t - cu_q[r];
+  if (TAPS > 0) taps = TAPS;
   const int K = taps - 1;
   float* st = state + (size_t)slots[r] * K * C + c;
   float acc[8], cur[8];
+  uint4 wraw[TAPS > 0 ? TAPS : 1];                  // the filters of channels c .. c + 7 lie together: 8 * taps values
+  if (TAPS > 0) {
+#pragma unroll
+    for (int u = 0; u < TAPS; ++u) wraw[u] = *reinterpret_cast<const uint4*>(w + (size_t)c * TAPS + u * 8);
+  }
+  const __nv_bfloat16* wl = reinterpret_cast<const __nv_bfloat16*>(wraw);
 #pragma unroll
   for (int e = 0; e < 8; ++e) { acc[e] = bias ? to_float(bias[c + e]) : 0.f; cur[e] = 0.f; }
-  for (int j = 0; j < taps; ++j) {
+#pragma unroll
+  for (int j = 0; j < (TAPS > 0 ? TAPS : taps); ++j) {
     const int src = i - K + j;
     if (src >= 0) {
       const uint4 raw = *reinterpret_cast<const uint4*>(x + (size_t)(t - K + j) * x_stride + c);
@@ -84,7 +93,7 @@ __global__ void __launch_bounds__(CONV_THREADS) causal_conv8_kernel(
       cur[0] = a.x; cur[1] = a.y; cur[2] = a.z; cur[3] = a.w; cur[4] = b.x; cur[5] = b.y; cur[6] = b.z; cur[7] = b.w;
     }
 #pragma unroll
-    for (int e = 0; e < 8; ++e) acc[e] += to_float(w[(size_t)(c + e) * taps + j]) * cur[e];
+    for (int e = 0; e < 8; ++e) acc[e] += (TAPS > 0 ? to_float(wl[e * TAPS + j]) : to_float(w[(size_t)(c + e) * taps + j])) * cur[e];
   }
   uint4 packed;
   __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(&packed);
@@ -498,11 +507,13 @@ SB_EXPORT int sb_causal_conv(const void* x, int x_stride, const void* w, const v
   } else if (dtype == SB_DTYPE_BF16) {
     typedef __nv_bfloat16 B;
     const bool by8 = C % 8 == 0 && x_stride % 8 == 0 && out_stride % 8 == 0 && aligned16(x) && aligned16(out) && (!state || aligned16(state));
-    if (by8)
-      causal_conv8_kernel<<<dim3((C / 8 + CONV_THREADS - 1) / CONV_THREADS, n_tokens), CONV_THREADS, 0, stream>>>(
+    if (by8) {
+      auto k8 = causal_conv8_kernel<0>;
+      if (aligned16(w)) k8 = taps == 2 ? causal_conv8_kernel<2> : taps == 3 ? causal_conv8_kernel<3> : taps == 4 ? causal_conv8_kernel<4> : k8;
+      k8<<<dim3((C / 8 + CONV_THREADS - 1) / CONV_THREADS, n_tokens), CONV_THREADS, 0, stream>>>(
           (const B*)x, x_stride, (const B*)w, (const B*)bias, state, slots, cu_q, token_row, (B*)out, out_stride, C, taps, act, residual,
           pure_decode);
-    else
+    } else
       causal_conv_kernel<B><<<grid, CONV_THREADS, 0, stream>>>((const B*)x, x_stride, (const B*)w, (const B*)bias, state, slots, cu_q,
                                                                 token_row, (B*)out, out_stride, C, taps, act, residual, pure_decode);
     SB_LAUNCH_CHECK();

@@ -379,8 +379,12 @@ class CudaKernels:
     def attention(self, qkv, k_cache, v_cache, block_table, cu_q, kv_len, token_row, positions, heads, kv_heads, head_dim,
                   page_size, scale, window, out, shape, slopes=None, chunk: int = 0) -> None:
         """``slopes`` (float [heads]): slope_h * distance is taken off every score; ``chunk`` > 0: a query sees only the keys of
-        its own block of ``chunk`` positions. Both run on the plain-arithmetic kernel, in either dtype."""
+        its own block of ``chunk`` positions. In bfloat16 both run on the mma.sync kernels (the tensor-memory kernel takes
+        neither), in float32 on the plain-arithmetic kernel."""
         lib = self._attention_lib(head_dim)
+        if (slopes is not None or chunk) and qkv.dtype == torch.bfloat16 and not self.force_simt_attention:
+            return self._attention_mma(lib, qkv, k_cache, v_cache, block_table, cu_q, kv_len, heads, kv_heads, head_dim,
+                                       page_size, scale, window, out, shape, slopes=slopes, chunk=int(chunk))
         if slopes is not None or chunk:
             group = heads // kv_heads
             self.launches += (1 if group <= 16 else 0) + (1 if group > 16 or shape.max_q * group > 16 else 0)
@@ -412,7 +416,7 @@ class CudaKernels:
         return max(1, min(want, -(-max_kv // 256), self.MAX_SPLITS))
 
     def _attention_mma(self, lib, qkv, k_cache, v_cache, block_table, cu_q, kv_len, heads, kv_heads, head_dim, page_size,
-                       scale, window, out, shape) -> None:
+                       scale, window, out, shape, slopes=None, chunk: int = 0) -> None:
         group = heads // kv_heads
         min_q = getattr(shape, "min_q", 1)
         which = 0
@@ -439,7 +443,8 @@ class CudaKernels:
             if num_splits > 1:
                 scratch = self._scratch_buffer(lib, shape.rows, kv_heads, num_splits)
                 tickets = self._ticket_buffer(shape.rows * kv_heads)
-        if (which & 1) and self.use_tcgen05_attention and self._tc_attention_takes(lib, heads, kv_heads, head_dim, page_size, window, qkv.shape[1]):
+        by_distance = slopes is not None or chunk > 0
+        if (which & 1) and not by_distance and self.use_tcgen05_attention and self._tc_attention_takes(lib, heads, kv_heads, head_dim, page_size, window, qkv.shape[1]):
             # prompt portions on the tensor-memory path; what is left (decoding rows) goes to the deep shape below
             self.launches += 1
             _check(lib.sb_attention_tc(
@@ -451,10 +456,11 @@ class CudaKernels:
             if not which:
                 return
         self.launches += (which & 1) + ((which >> 1) & 1) + ((which >> 2) & 1)
-        _check(lib.sb_attention_mma(
-            _p(qkv), qkv.shape[1], _p(k_cache), _p(v_cache), _p(block_table), block_table.shape[1], _p(cu_q), _p(kv_len),
+        _check(lib.sb_attention_mma_biased(
+            _p(qkv), qkv.stride(0), _p(k_cache), _p(v_cache), _p(block_table), block_table.shape[1], _p(cu_q), _p(kv_len),
             heads, kv_heads, page_size, k_cache.shape[0], ctypes.c_float(scale), window, _p(out), shape.rows, shape.max_q,
-            which, int(shape.max_kv), num_splits, _p(scratch), _p(tickets), _p(wide_rows), n_wide, self._s()), "attention")
+            which, int(shape.max_kv), num_splits, _p(scratch), _p(tickets), _p(wide_rows), n_wide, _p(slopes), chunk, self._s()),
+            "attention")
 
     def _tc_attention_takes(self, lib, heads, kv_heads, head_dim, page_size, window, stride) -> bool:
         key = (heads, kv_heads, head_dim, page_size, window, stride)
