@@ -1,4 +1,4 @@
-"""serve_b200: a small, whole inference engine for one B200, for the Llama dense decoder.
+"""serve_b200: a small, whole inference engine for one B200, for the Llama dense decoder and the Rogisun decoder.
 
 From a model folder (config.json + safetensors) or seeded random weights to
 generated tokens: typed configuration and architecture registry, weights by

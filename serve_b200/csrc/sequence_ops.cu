@@ -307,6 +307,7 @@ __global__ void __launch_bounds__(REC_THREADS) recurrence_scan_kernel(RecArgs a)
     __syncthreads();                                                  // this stage has arrived for every thread
     const float* base = smem + (size_t)stage * stage_floats;
     const int nt = min(REC_TS, n - t0);
+#pragma unroll 2      // the sums of one token's read-out overlap with the next token's update
     for (int tt = 0; tt < nt; ++tt) {
       const float4* q4 = reinterpret_cast<const float4*>(base + (size_t)tt * per_tok);
       const float4* k4 = q4 + dkp / 4;

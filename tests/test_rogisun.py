@@ -419,3 +419,23 @@ def test_pages_behind_a_block_of_positions_go_back_to_the_pool():
     assert mgr.peak_pages(1000, 1) == [(24 + 1 - 2) // 8 + 2]
     mgr.close("a")
     assert mgr.groups[0].pool.in_use == 0
+
+
+def test_named_states_are_cleared_when_a_slot_is_handed_out_again():
+    """A layer's states (a recurrence's matrix, the tails of its convolutions) are rows of [max_slots, ...] tensors; a
+    request that gets a slot somebody else held must find zeros, and a part sees its own states under its prefix."""
+    from serve_b200.parts import CacheNeed
+
+    need = CacheNeed.merged([("", CacheNeed(states=(("state", (2, 3, 4)),))), ("mixer_filter.", CacheNeed(states=(("tail", (2, 5)),))),
+                             ("right.", CacheNeed(state_shape=(7,)))])
+    assert dict(need.states) == {"state": (2, 3, 4), "mixer_filter.tail": (2, 5), "right.state": (7,)} and not need.has_pages
+    mgr = CacheManager([need], [None], 8, 4, 2, 64, device="cpu", kv_dtype=torch.float32)
+    view = mgr.views()[0]
+    assert set(view.states) == {"state", "mixer_filter.tail", "right.state"} and view.states["state"].shape == (2, 2, 3, 4)
+    assert set(view.sub("mixer_filter.").states) == {"tail"} and view.sub("right.").state is view.states["right.state"]
+    slot = mgr.open("a")
+    for st in view.states.values():
+        st[slot].fill_(3.0)
+    mgr.close("a")
+    assert mgr.open("b") == slot
+    assert all(float(st[slot].abs().max()) == 0.0 for st in view.states.values())
