@@ -370,11 +370,35 @@ def kernel_times(eng, entries, end):
     return sorted(((k, n, round(us, 1)) for k, (n, us) in total.items()), key=lambda r: -r[2])
 
 
+def prefill_many(eng, vocab, requests, each, reps=5, seed=11):
+    """One step that brings ``requests`` prompts of ``each`` tokens (median of ``reps`` after two untimed steps)."""
+    import torch
+    from serve_b200.engine import StepEntry
+
+    g = torch.Generator().manual_seed(seed)
+    times = []
+    for i in range(reps + 2):
+        entries = [StepEntry(f"m{i}-{j}", torch.randint(0, vocab, (each,), generator=g).tolist(), [each - 1]) for j in range(requests)]
+        torch.cuda.synchronize()
+        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        ev0.record()
+        eng.step(entries)
+        ev1.record()
+        torch.cuda.synchronize()
+        for e in entries:
+            eng.end(e.rid)
+        if i >= 2:
+            times.append(ev0.elapsed_time(ev1))
+    times.sort()
+    return times[len(times) // 2]
+
+
 def design_bench(args):
     """Prefill (one prompt of 2,048 tokens) and decode (batch 8 after 2,048-token prompts, from CUDA graphs) of Rogisun and of
     the Llama decoder of equal size, at each width asked for, bfloat16, random weights; CUDA events on the stream, the
-    weights alone exceed the L2 cache. Prints one JSON line: per width and design the two rates and the kernels of one prompt
-    step and one (eager) decoding step with their device times."""
+    weights alone exceed the L2 cache. Prints one JSON line: per width and design the two rates, the rate of a step of 8 prompts
+    of 256 tokens (the same tokens side by side: what a recurrence walks in turn for one prompt it walks at once for eight),
+    and the kernels of one prompt step and one (eager) decoding step with their device times."""
     import torch
 
     from serve_b200.config import EngineConfig
@@ -395,6 +419,7 @@ def design_bench(args):
                 sampler = Sampler(eng.kernels, eng.rt.device, seed=0)
                 vocab = eng.spec.vocab_size
                 pre_ms = prefill_bench(eng, vocab, reps=5, seed=7)
+                many_ms = prefill_many(eng, vocab, 8, PREFILL_TOKENS // 8)
                 ms, _ctx, launches, lib_calls = decode_bench(eng, sampler, batch, args.steps, max(args.warmup, 3), vocab, seed=1)
                 g = torch.Generator().manual_seed(5)
                 toks = torch.randint(0, vocab, (PREFILL_TOKENS,), generator=g).tolist()
@@ -405,6 +430,7 @@ def design_bench(args):
                     eng.step([StepEntry(rid, toks[:PROMPT_LEN - 8], [])])
                 decode_kernels = kernel_times(eng, [StepEntry(rid, [1], [0]) for rid in rids], rids)
             rec[name] = {"prefill_tokens_per_s": round(PREFILL_TOKENS / (pre_ms * 1e-3), 1), "prefill_ms": round(pre_ms, 3),
+                         "prefill_8_prompts_ms": round(many_ms, 3), "prefill_8_prompts_tokens_per_s": round(PREFILL_TOKENS / (many_ms * 1e-3), 1),
                          "decode_tokens_per_s": round(batch * 1000.0 / ms, 1), "decode_ms_per_step": round(ms, 4),
                          "gpu_launches": int(launches), "library_gemm_calls": int(lib_calls),
                          "prompt_step_kernels": prompt_kernels[:14], "decode_step_kernels": decode_kernels[:14]}

@@ -235,7 +235,8 @@ class EmuKernels:
         m = self.math
         z = logits.to(torch.float32)
         scores = torch.sigmoid(z) if score == "sigmoid" else torch.softmax(z, -1)
-        wts, idx = torch.topk(scores, top, dim=-1)
+        idx = torch.topk(z, top, dim=-1).indices                 # by logit: scores of large logits round to ties
+        wts = torch.gather(scores, 1, idx)
         if renormalise:
             wts = wts / wts.sum(-1, keepdim=True)
         ff = w_down.shape[2]

@@ -158,7 +158,7 @@ def routed_experts(h, w, p, f, margins: list = None):
     n, top, limit = f["router"]["experts"], f["router"]["top"], f["expert"]["limit"]
     z = h @ w[p + "router"].T
     scores = torch.sigmoid(z)
-    best = torch.topk(scores, top, dim=-1).indices
+    best = torch.topk(z, top, dim=-1).indices          # the largest scores are the largest logits (sigmoid rounds big ones to ties)
     if margins is not None and top < n:
         ranked = torch.sort(z, dim=-1, descending=True).values
         margins.append(float((ranked[:, top - 1] - ranked[:, top]).min()))

@@ -30,6 +30,19 @@ CONFIGS = {
             "left_scale": 0.7, "right_scale": 1.3}, "mlp": None},
         {"type": "mamba2", "mixer": {"heads": 4, "vdim": 8, "state": 12, "groups": 2, "norm_groups": 2, "conv": 3}, "mlp": MOE(3, 1, 16, 0.8)},
     ]},
+    # sizes that are multiples of nothing: no vector load, no tensor-core tile and no padded head fits them exactly
+    "o": {"architecture": "Rogisun", "width": 100, "vocab": 131, "norm": {"eps": 3e-5}, "canon": {"taps": 5}, "layers": [
+        {"type": "mamba2", "mixer": {"heads": 5, "vdim": 6, "state": 10, "groups": 5, "norm_groups": 3, "conv": 3}, "mlp": MOE(7, 2, 22, 1.1)},
+        {"type": "lightning", "mixer": {"heads": 5, "dim": 12, "vdim": 20, "decay": [0.7, 0.8, 0.9, 0.95, 0.99]}, "mlp": None},
+        {"type": "parallel", "mixer": {
+            "left": {"heads": 6, "kv_heads": 2, "dim": 20, "vdim": 12, "scale": 0.2, "mask": {"size": 17}},
+            "right": {"heads": 3, "kv_heads": 3, "dim": 12, "vdim": 10, "conv": 5, "rank": 7},
+            "left_scale": 0.9, "right_scale": 0.8}, "mlp": MOE(3, 3, 30, 0.9)},
+        {"type": "parallel", "mixer": {
+            "left": {"heads": 2, "kv_heads": 1, "dim": 40, "vdim": 40, "scale": 0.15, "mask": {"size": 64}},
+            "right": {"heads": 4, "kv_heads": 1, "dim": 20, "vdim": 6, "conv": 2, "rank": 3},
+            "left_scale": 0.4, "right_scale": 1.1}, "mlp": MOE(4, 1, 18, 3.0)},
+    ]},
     "q": {"architecture": "Rogisun", "width": 48, "vocab": 97, "norm": {"eps": 1e-6}, "canon": {"taps": 2}, "layers": [
         {"type": "parallel", "mixer": {
             "left": {"heads": 3, "kv_heads": 3, "dim": 24, "vdim": 16, "scale": 0.25, "mask": {"size": 10}},

@@ -16,8 +16,8 @@ from tests import helpers
 from tests.plain import rogisun_plain as P
 from tests.rogisun_cases import BACKENDS, CONFIGS, compare_rows, make_engine, make_weights, plain_logits, runtime_for, settled_weights, tolerance, write_model
 
-LENGTHS = {"p": [1, 5, 23, 49, 75, 130], "q": [2, 9, 31, 64, 101]}
-PAGE = {"p": 8, "q": 16}
+LENGTHS = {"p": [1, 5, 23, 49, 75, 130], "q": [2, 9, 31, 64, 101], "o": [3, 40, 90]}
+PAGE = {"p": 8, "q": 16, "o": 4}
 
 
 # ---- configuration and description ----------------------------------------------------------------------------
@@ -82,7 +82,7 @@ def models(tmp_path_factory):
 
 
 @pytest.mark.parametrize("backend", BACKENDS)
-@pytest.mark.parametrize("name", ["p", "q"])
+@pytest.mark.parametrize("name", ["p", "q", "o"])
 @pytest.mark.parametrize("cut", ["whole", "tail_decode", "portions", "single_tokens"])
 def test_cuts_match_plain(models, name, backend, cut):
     w, reqs, plain, folders = models[name]
@@ -103,7 +103,7 @@ def test_cuts_match_plain(models, name, backend, cut):
 
 
 @pytest.mark.parametrize("backend", BACKENDS)
-@pytest.mark.parametrize("name", ["p", "q"])
+@pytest.mark.parametrize("name", ["p", "q", "o"])
 def test_mixed_batches_with_pages_and_slots_used_again(models, name, backend):
     """Unequal requests side by side, portions beside single tokens, fewer slots and pages than requests: every
     row must equal the request run alone. Pages and states are poisoned first, so that a page or a state that is
@@ -115,7 +115,7 @@ def test_mixed_batches_with_pages_and_slots_used_again(models, name, backend):
     assert need < sum(-(-len(t) // page) for t in reqs.values())
     # behind the start of a query's block of positions no key is read again: the cache manager gives those pages back at
     # once, so three live requests get by with what a block and a portion span, far fewer pages than their tokens
-    block = next(l["mixer"]["left"]["mask"]["size"] for l in CONFIGS[name]["layers"] if l["type"] == "parallel")
+    block = max(l["mixer"]["left"]["mask"]["size"] for l in CONFIGS[name]["layers"] if l["type"] == "parallel")
     pool = min(need, 3 * CacheManager.most_pages_of_a_request(None, page, 160, 21, block))
     assert pool < sum(-(-len(t) // page) for t in reqs.values())
     eng = make_engine(folders[backend[1]], backend, page, num_pages=pool, max_slots=3, context=160)
