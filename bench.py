@@ -423,6 +423,9 @@ def design_bench(args):
                 ms, _ctx, launches, lib_calls = decode_bench(eng, sampler, batch, args.steps, max(args.warmup, 3), vocab, seed=1)
                 g = torch.Generator().manual_seed(5)
                 toks = torch.randint(0, vocab, (PREFILL_TOKENS,), generator=g).tolist()
+                each = PREFILL_TOKENS // 8
+                many = [StepEntry(f"mk{j}", toks[j * each:(j + 1) * each], [each - 1]) for j in range(8)]
+                many_kernels = kernel_times(eng, many, [e.rid for e in many])
                 prompt_kernels = kernel_times(eng, [StepEntry("k", toks, [PREFILL_TOKENS - 1])], [])
                 eng.stepper.use_cuda_graphs = False
                 rids = ["k"] + [f"k{i}" for i in range(1, batch)]
@@ -433,7 +436,8 @@ def design_bench(args):
                          "prefill_8_prompts_ms": round(many_ms, 3), "prefill_8_prompts_tokens_per_s": round(PREFILL_TOKENS / (many_ms * 1e-3), 1),
                          "decode_tokens_per_s": round(batch * 1000.0 / ms, 1), "decode_ms_per_step": round(ms, 4),
                          "gpu_launches": int(launches), "library_gemm_calls": int(lib_calls),
-                         "prompt_step_kernels": prompt_kernels[:14], "decode_step_kernels": decode_kernels[:14]}
+                         "prompt_step_kernels": prompt_kernels[:14], "prompts_8_step_kernels": many_kernels[:14],
+                         "decode_step_kernels": decode_kernels[:14]}
             del eng, sampler
             torch.cuda.empty_cache()
         out["sizes"][str(width)] = rec

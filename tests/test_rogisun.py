@@ -72,12 +72,16 @@ def test_a_file_decides_the_width_of_the_two_step_projections(tmp_path):
 # ---- whole models under every way of cutting the work ------------------------------------------------------------
 @pytest.fixture(scope="module")
 def models(tmp_path_factory):
+    """{config name: {dtype: (weights, requests, plain logits, model folder)}}; the bfloat16 models have damped experts
+    (rogisun_cases.settled_weights says why)."""
     out = {}
-    for name, cfg in CONFIGS.items():
+    for name in LENGTHS:
+        cfg = CONFIGS[name]
         reqs = {f"r{i}": helpers.random_tokens(cfg["vocab"], n, seed=20 + i) for i, n in enumerate(LENGTHS[name])}
-        w, plain = settled_weights(cfg, reqs)
-        out[name] = (w, reqs, plain, {dt: write_model(str(tmp_path_factory.mktemp(f"{name}-{dt}")), cfg, w, getattr(torch, dt))
-                                      for dt in ("float32", "bfloat16")})
+        out[name] = {}
+        for dt, gain in (("float32", 1.0), ("bfloat16", 0.1)):
+            w, plain = settled_weights(cfg, reqs, min_margin=0.05 if gain == 1.0 else 0.0, expert_gain=gain)
+            out[name][dt] = (w, reqs, plain, write_model(str(tmp_path_factory.mktemp(f"{name}-{dt}")), cfg, w, getattr(torch, dt)))
     return out
 
 
@@ -85,9 +89,9 @@ def models(tmp_path_factory):
 @pytest.mark.parametrize("name", ["p", "q", "o"])
 @pytest.mark.parametrize("cut", ["whole", "tail_decode", "portions", "single_tokens"])
 def test_cuts_match_plain(models, name, backend, cut):
-    w, reqs, plain, folders = models[name]
+    w, reqs, plain, folder = models[name][backend[1]]
     page = PAGE[name]
-    eng = make_engine(folders[backend[1]], backend, page, num_pages=-(-160 // page) * 2, graphs=(cut == "tail_decode"))
+    eng = make_engine(folder, backend, page, num_pages=-(-160 // page) * 2, graphs=(cut == "tail_decode"))
     if cut == "single_tokens":
         steps = helpers.trace_tail_decode({k: v for k, v in reqs.items() if len(v) <= 50}, tail=10 ** 6)
     else:
@@ -108,7 +112,7 @@ def test_mixed_batches_with_pages_and_slots_used_again(models, name, backend):
     """Unequal requests side by side, portions beside single tokens, fewer slots and pages than requests: every
     row must equal the request run alone. Pages and states are poisoned first, so that a page or a state that is
     read without having been written (or cleared) shows."""
-    w, reqs, plain, folders = models[name]
+    w, reqs, plain, folder = models[name][backend[1]]
     page = PAGE[name]
     steps = helpers.trace_mixed(reqs, live=3, seed=7)
     need = helpers.tokens_needed(steps, page) // page
@@ -118,7 +122,7 @@ def test_mixed_batches_with_pages_and_slots_used_again(models, name, backend):
     block = max(l["mixer"]["left"]["mask"]["size"] for l in CONFIGS[name]["layers"] if l["type"] == "parallel")
     pool = min(need, 3 * CacheManager.most_pages_of_a_request(None, page, 160, 21, block))
     assert pool < sum(-(-len(t) // page) for t in reqs.values())
-    eng = make_engine(folders[backend[1]], backend, page, num_pages=pool, max_slots=3, context=160)
+    eng = make_engine(folder, backend, page, num_pages=pool, max_slots=3, context=160)
     for view in eng.stepper.views:
         if view.k is not None:
             view.k.fill_(float("nan"))
@@ -139,10 +143,10 @@ def test_long_decoding_side_by_side(models, backend):
     """Two requests decoded one token at a time for 120 steps after short prompts (from CUDA graphs on the GPU): the
     states are carried through every step, and the blocks of positions and the pages are crossed many times."""
     cfg = CONFIGS["q"]
-    w = models["q"][0]
+    w, _, _, folder = models["q"][backend[1]]
     seqs = {f"d{i}": helpers.random_tokens(cfg["vocab"], 140 - 9 * i, seed=60 + i) for i in range(2)}
     plain = {rid: plain_logits(w, cfg, toks) for rid, toks in seqs.items()}
-    eng = make_engine(models["q"][3][backend[1]], backend, 16, num_pages=24, graphs=True)
+    eng = make_engine(folder, backend, 16, num_pages=24, graphs=True)
     steps = [{"step": 0, "entries": [{"id": rid, "tokens": t[:11 + 6 * i], "want": [10 + 6 * i]} for i, (rid, t) in enumerate(seqs.items())], "end": []}]
     at = {rid: 11 + 6 * i for i, rid in enumerate(seqs)}
     while any(at[rid] < len(seqs[rid]) for rid in seqs):
@@ -165,15 +169,15 @@ def test_greedy_generation_through_the_scheduler(models, backend):
     from serve_b200.run import Request, generate
 
     cfg = CONFIGS["p"]
-    w, reqs, _, folders = models["p"]
-    eng = make_engine(folders[backend[1]], backend, 8, num_pages=40, max_slots=3, budget=32)
+    w, reqs, _, folder = models["p"][backend[1]]
+    eng = make_engine(folder, backend, 8, num_pages=40, max_slots=3, budget=32)
     prompts = [reqs["r1"], reqs["r2"], reqs["r3"][:30], reqs["r0"]]
     out = generate(eng, [Request(torch.tensor(p), len(p), 12) for p in prompts], temperature=0.0, eos_token_id=None)
     for p, r in zip(prompts, out):
         new = r.generated_tokens.tolist()
         assert len(new) == 12
         logits = plain_logits(w, cfg, p + new)
-        tol = float(logits.abs().max()) * (2e-4 if backend[1] == "float32" else 2.0 ** -5)
+        tol = float(logits.abs().max()) * (2e-4 if backend[1] == "float32" else 2.0 ** -4)
         for i, tok in enumerate(new):
             row = logits[len(p) - 1 + i]
             assert float(row[tok]) >= float(row.max()) - 2 * tol, f"token {i} of a request is not the plain model's choice"
@@ -204,7 +208,7 @@ def _run_part(backend, family, spec, weights, x, cuts, page=8):
     names = {d.name for d in part.tensor_decls()}
     part.load({n: weights[n].to(dev).to(rt.act_dtype) for n in names})
     need = part.cache_need() if hasattr(part, "cache_need") else None
-    mgr = CacheManager([need], [None], page, 64, 1, 512, device=dev, kv_dtype=rt.act_dtype)
+    mgr = CacheManager([need], [None], page, 128, 1, 1024, device=dev, kv_dtype=rt.act_dtype)
     view = mgr.views()[0]
 
     def call(h, ctx):
@@ -280,6 +284,31 @@ def test_mamba2_mixer_alone(backend, cuts, where):
 @pytest.mark.parametrize("where", [("p", 1), ("q", 0)], ids=["p", "q"])
 def test_parallel_mixer_alone(backend, cuts, where):
     _mixer_case(backend, where[0], where[1], cuts)
+
+
+@pytest.mark.parametrize("backend", BACKENDS[1:])
+@pytest.mark.parametrize("index", [0, 1, 2], ids=["lightning", "mamba2", "parallel"])
+@pytest.mark.parametrize("cuts", [[420], [130, 1, 1, 270, 18]], ids=["whole", "portions"])
+def test_mixers_at_the_sizes_of_a_real_layer(backend, index, cuts):
+    """Each mixer alone at heads of 128 and states of 128 rows, over 420 tokens (the block of 256 positions is crossed, the
+    recurrences' staging ring turns many times), whole and cut with single tokens in the middle."""
+    _mixer_case(backend, "wide", index, cuts, seed=31)
+
+
+@pytest.mark.parametrize("backend", BACKENDS[1:])
+def test_experts_at_the_sizes_of_a_real_layer(backend):
+    from serve_b200.models.rogisun import rogisun_spec
+
+    cfg, layer, p = _layer("wide", 0)
+    w = make_weights(cfg, 33)
+    spec = rogisun_spec(config_from_dict(cfg)).layers[0].parts["feed_forward"]
+    x = torch.randn(700, cfg["width"], generator=torch.Generator().manual_seed(3)).bfloat16().float()
+    want = P.routed_experts(x.double(), {k: v.double() for k, v in w.items()}, p + "mlp.", layer["mlp"]).float()
+    z = x.double() @ w[p + "mlp.router"].double().T
+    keep = (torch.sort(z, descending=True).values[:, 1:3].diff(dim=1).abs() >= 0.08).flatten()      # no close call between 2nd and 3rd
+    got = _run_part(backend, "feed_forward", spec, w, x, [700], page=16)
+    assert int(keep.sum()) > 550
+    torch.testing.assert_close(got[keep], want[keep], atol=_tol(backend, want), rtol=0)
 
 
 @pytest.mark.parametrize("backend", BACKENDS)
@@ -439,3 +468,48 @@ def test_named_states_are_cleared_when_a_slot_is_handed_out_again():
     mgr.close("a")
     assert mgr.open("b") == slot
     assert all(float(st[slot].abs().max()) == 0.0 for st in view.states.values())
+
+
+@pytest.mark.gpu
+def test_trace_run_and_command_line_programs(models, tmp_path):
+    """bin/trace_run and `python -m serve_b200.run` as a user starts them, on a model folder of this design: the class is
+    chosen by config.json, four state slots and a pool smaller than the requests' total, so slots and pages come again."""
+    import json
+    import os
+    import subprocess
+    import sys
+
+    import numpy as np
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    for dtype in ("float32", "bfloat16"):
+        w, reqs, plain, folder = models["q"][dtype]
+        steps = helpers.trace_mixed(reqs, live=4, seed=9)
+        need = helpers.tokens_needed(steps, 64)
+        out_dir = tmp_path / f"out-{dtype}"
+        proc = subprocess.run([os.path.join(root, "bin", "trace_run"), "--model", folder, "--dtype", dtype, "--out", str(out_dir),
+                               "--max-tokens", str(need)], input="\n".join(json.dumps(s) for s in steps) + "\n",
+                              capture_output=True, text=True, timeout=900)
+        assert proc.returncode == 0, proc.stderr[-3000:]
+        assert [l for l in proc.stdout.splitlines() if l.startswith("done")] == [f"done {s['step']}" for s in steps]
+        got, at = {}, {}
+        for s in steps:
+            n_want = sum(len(e["want"]) for e in s["entries"])
+            arr = np.fromfile(out_dir / f"{s['step']}.f32", dtype="<f4").reshape(n_want, CONFIGS["q"]["vocab"])
+            i = 0
+            for e in s["entries"]:
+                base = at.get(e["id"], 0)
+                for wi in e["want"]:
+                    got[(e["id"], base + wi)] = torch.from_numpy(arr[i].copy())
+                    i += 1
+                at[e["id"]] = base + len(e["tokens"])
+        compare_rows(got, plain, ("cuda", dtype))
+    w, reqs, plain, folder = models["q"]["float32"]
+    prompt = reqs["r2"]
+    out = subprocess.run([sys.executable, "-m", "serve_b200.run", "--model", folder, "--dtype", "float32", "--page-size", "8", "--num-pages",
+                          "16", "--max-context", "64", "--max-slots", "2", "--prompt-ids", ",".join(map(str, prompt)), "--max-new-tokens", "4"],
+                         cwd=root, capture_output=True, text=True, timeout=600)
+    assert out.returncode == 0, out.stderr[-2000:]
+    new = json.loads([l for l in out.stdout.splitlines() if l.startswith("{")][-1])["generated_tokens"]
+    logits = plain_logits(w, CONFIGS["q"], prompt + new)
+    assert all(int(logits[len(prompt) - 1 + i].argmax()) == t for i, t in enumerate(new))
