@@ -15,7 +15,8 @@ so the table is [slot, block].
 
 A request holds one *slot* while it lives: a row of every group's block table,
 and a row of every fixed-size state tensor [max_slots, ...] that a mixer asked
-for (zeroed when the slot is handed out). Llama asks for none.
+for (all of them column slices of one [max_slots, total] tensor, whose row is
+zeroed when the slot is handed out). Llama asks for none.
 
 Pages are given back when a request closes, and earlier when a group has a
 window and the request has moved past a page. Block tables are kept on the
@@ -130,8 +131,32 @@ class CacheManager:
         self._kv: List[Optional[Tuple[object, object]]] = [None] * len(needs)
         self._state: List[object] = [None] * len(needs)
         self._states: List[Dict[str, object]] = [{} for _ in needs]
+        self._state_pool = None       # [max_slots, floats of all states]: every state tensor is a slice of its columns
         if device is not None:
             import torch
+
+            # All states of a slot lie in one row of one tensor, so handing a slot out clears them with one launch however
+            # many layers keep state. (Rows are padded to 16 bytes; a state's own rows stay contiguous, slots are a row apart.)
+            sizes = []
+            for need in needs:
+                if need is None:
+                    continue
+                for shape in ([need.state_shape] if need.state_shape is not None else []) + [sh for _, sh in need.states]:
+                    n = 1
+                    for d in shape:
+                        n *= int(d)
+                    sizes.append(-(-n // 4) * 4)
+            if sizes:
+                self._state_pool = torch.zeros((max_slots, sum(sizes)), dtype=torch.float32, device=device)
+            at = [0]
+
+            def carve(shape):
+                n = 1
+                for d in shape:
+                    n *= int(d)
+                view = self._state_pool[:, at[0]: at[0] + n].view((max_slots,) + tuple(int(d) for d in shape))
+                at[0] += -(-n // 4) * 4
+                return view
 
             for i, need in enumerate(needs):
                 if need is None:
@@ -141,9 +166,9 @@ class CacheManager:
                     self._kv[i] = (torch.zeros(shape, dtype=kv_dtype, device=device),
                                    torch.zeros(shape, dtype=kv_dtype, device=device))
                 if need.state_shape is not None:
-                    self._state[i] = torch.zeros((max_slots,) + tuple(need.state_shape), dtype=torch.float32, device=device)
+                    self._state[i] = carve(need.state_shape)
                 for name, shape in need.states:
-                    self._states[i][name] = torch.zeros((max_slots,) + tuple(shape), dtype=torch.float32, device=device)
+                    self._states[i][name] = carve(shape)
 
     # ---- sizes ----------------------------------------------------------
     @staticmethod
@@ -236,12 +261,8 @@ class CacheManager:
             raise NoFreeSlot(f"all {self.max_slots} slots are in use")
         slot = self._free_slots.pop()
         self._requests[rid] = _Request(slot, 0, [0] * len(self.groups), [0] * len(self.groups))
-        for st in self._state:
-            if st is not None:
-                st[slot].zero_()
-        for named in self._states:
-            for st in named.values():
-                st[slot].zero_()
+        if self._state_pool is not None:
+            self._state_pool[slot].zero_()
         return slot
 
     def _first_needed_block(self, g: _Group, length_before: int) -> int:

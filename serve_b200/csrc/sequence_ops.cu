@@ -23,7 +23,7 @@ __device__ __forceinline__ float load_w(const void* p, int dtype, size_t i) {
 // ------------------------------------------------------------------------------------------ short convolution
 // out[t, c] = act( bias[c] + sum_j w[c, j] * in[t - taps + 1 + j, c]  (+ in[t, c] if residual) ), in[-1], in[-2], ...
 // of a row's first token being the inputs the state holds: state[slot, m, c] is the input taps - 1 - m tokens
-// before the portion's start. With inline_state (every row brings one token) the thread also shifts the state.
+// before the portion's start (slots are slot_stride floats apart: the states of a slot may lie in one row of a pool). With inline_state (every row brings one token) the thread also shifts the state.
 constexpr int CONV_THREADS = 128;
 constexpr int CONV_MAX_TAPS = 16;
 
@@ -31,14 +31,14 @@ template <typename T>
 __global__ void __launch_bounds__(CONV_THREADS) causal_conv_kernel(
     const T* __restrict__ x, int x_stride, const T* __restrict__ w, const T* __restrict__ bias, float* __restrict__ state,
     const int* __restrict__ slots, const int* __restrict__ cu_q, const int* __restrict__ token_row, T* __restrict__ out,
-    int out_stride, int C, int taps, int act, int residual, int inline_state) {
+    int out_stride, int C, int taps, int act, int residual, int inline_state, long long slot_stride) {
   const int c = blockIdx.x * CONV_THREADS + threadIdx.x;
   const int t = blockIdx.y;
   if (c >= C) return;
   const int r = token_row[t];
   const int i = t - cu_q[r];
   const int K = taps - 1;
-  float* st = state + (size_t)slots[r] * K * C + c;
+  float* st = state + (size_t)slots[r] * slot_stride + c;
   float acc = bias ? to_float(bias[c]) : 0.f;
   float cur = 0.f;
   for (int j = 0; j < taps; ++j) {
@@ -62,7 +62,7 @@ template <int TAPS>      // the number of taps when it is 2, 3 or 4 (the eight f
 __global__ void __launch_bounds__(CONV_THREADS) causal_conv8_kernel(
     const __nv_bfloat16* __restrict__ x, int x_stride, const __nv_bfloat16* __restrict__ w, const __nv_bfloat16* __restrict__ bias,
     float* __restrict__ state, const int* __restrict__ slots, const int* __restrict__ cu_q, const int* __restrict__ token_row,
-    __nv_bfloat16* __restrict__ out, int out_stride, int C, int taps, int act, int residual, int inline_state) {
+    __nv_bfloat16* __restrict__ out, int out_stride, int C, int taps, int act, int residual, int inline_state, long long slot_stride) {
   const int c = (blockIdx.x * CONV_THREADS + threadIdx.x) * 8;
   const int t = blockIdx.y;
   if (c >= C) return;
@@ -70,7 +70,7 @@ __global__ void __launch_bounds__(CONV_THREADS) causal_conv8_kernel(
   const int i = t - cu_q[r];
   if (TAPS > 0) taps = TAPS;
   const int K = taps - 1;
-  float* st = state + (size_t)slots[r] * K * C + c;
+  float* st = state + (size_t)slots[r] * slot_stride + c;
   float acc[8], cur[8];
   uint4 wraw[TAPS > 0 ? TAPS : 1];                  // the filters of channels c .. c + 7 lie together: 8 * taps values
   if (TAPS > 0) {
@@ -120,13 +120,13 @@ __global__ void __launch_bounds__(CONV_THREADS) causal_conv8_kernel(
 template <typename T>
 __global__ void __launch_bounds__(CONV_THREADS) conv_state_kernel(const T* __restrict__ x, int x_stride, float* __restrict__ state,
                                                                    const int* __restrict__ slots, const int* __restrict__ cu_q, int C,
-                                                                   int taps) {
+                                                                   int taps, long long slot_stride) {
   const int c = blockIdx.x * CONV_THREADS + threadIdx.x;
   const int r = blockIdx.y;
   if (c >= C) return;
   const int q0 = cu_q[r], n = cu_q[r + 1] - q0;
   const int K = taps - 1;
-  float* st = state + (size_t)slots[r] * K * C + c;
+  float* st = state + (size_t)slots[r] * slot_stride + c;
   float keep[CONV_MAX_TAPS];
 #pragma unroll
   for (int m = 0; m < CONV_MAX_TAPS; ++m) {
@@ -167,7 +167,8 @@ struct RecArgs {
   const void* decay;                                 // DECAY: [H] float decays
   const void* a_log; const void* dt_bias; const void* d_skip;   // parameters (dtype par_dtype)
   int par_dtype;
-  float* state;                                      // [slots, H, dk, dv]
+  float* state;                                      // [slots, H, dk, dv], slots state_stride floats apart
+  long long state_stride;
   const int* slots; const int* cu_q;
   float* out; int out_stride;                        // [T, H * dv] float
   int H, Hqk, dk, dv, P, dkp, dvp, n_tokens;
@@ -264,7 +265,7 @@ __global__ void __launch_bounds__(REC_THREADS) recurrence_scan_kernel(RecArgs a)
   const bool col_ok = j < dv;
   const int q0 = a.cu_q[r], n = a.cu_q[r + 1] - q0;
   const int hq = h / (H / a.Hqk);
-  float* S = a.state + (((size_t)a.slots[r] * H + h) * dk) * dv;
+  float* S = a.state + (size_t)a.slots[r] * a.state_stride + ((size_t)h * dk) * dv;
   float s[REC_RPT];
 #pragma unroll
   for (int x = 0; x < REC_RPT; ++x) {
@@ -492,7 +493,7 @@ __global__ void __launch_bounds__(128) kv_norm_cache_write_kernel(const T* __res
 // token (pure_decode) moves the state in the same launch; otherwise a second launch does, after every read.
 SB_EXPORT int sb_causal_conv(const void* x, int x_stride, const void* w, const void* bias, float* state, const int* slots,
                              const int* cu_q, const int* token_row, void* out, int out_stride, int C, int taps, int act, int residual,
-                             int n_tokens, int n_rows, int pure_decode, int dtype, cudaStream_t stream) {
+                             int n_tokens, int n_rows, int pure_decode, long long slot_stride, int dtype, cudaStream_t stream) {
   if (n_tokens <= 0 || C <= 0) return 0;
   if (taps < 1 || taps > CONV_MAX_TAPS || n_rows <= 0 || n_rows > 65535 || n_tokens > 65535 * 32) return SB_ERR_LIMIT;
   if (x == out) return SB_ERR_SHAPE;
@@ -501,25 +502,26 @@ SB_EXPORT int sb_causal_conv(const void* x, int x_stride, const void* w, const v
   if (dtype == SB_DTYPE_F32) {
     causal_conv_kernel<float><<<grid, CONV_THREADS, 0, stream>>>((const float*)x, x_stride, (const float*)w, (const float*)bias, state,
                                                                   slots, cu_q, token_row, (float*)out, out_stride, C, taps, act, residual,
-                                                                  pure_decode);
+                                                                  pure_decode, slot_stride);
     SB_LAUNCH_CHECK();
     if (!pure_decode && taps > 1)
-      conv_state_kernel<float><<<sgrid, CONV_THREADS, 0, stream>>>((const float*)x, x_stride, state, slots, cu_q, C, taps);
+      conv_state_kernel<float><<<sgrid, CONV_THREADS, 0, stream>>>((const float*)x, x_stride, state, slots, cu_q, C, taps, slot_stride);
   } else if (dtype == SB_DTYPE_BF16) {
     typedef __nv_bfloat16 B;
-    const bool by8 = C % 8 == 0 && x_stride % 8 == 0 && out_stride % 8 == 0 && aligned16(x) && aligned16(out) && (!state || aligned16(state));
+    const bool by8 = C % 8 == 0 && x_stride % 8 == 0 && out_stride % 8 == 0 && aligned16(x) && aligned16(out) &&
+                     (!state || (aligned16(state) && slot_stride % 4 == 0));
     if (by8) {
       auto k8 = causal_conv8_kernel<0>;
       if (aligned16(w)) k8 = taps == 2 ? causal_conv8_kernel<2> : taps == 3 ? causal_conv8_kernel<3> : taps == 4 ? causal_conv8_kernel<4> : k8;
       k8<<<dim3((C / 8 + CONV_THREADS - 1) / CONV_THREADS, n_tokens), CONV_THREADS, 0, stream>>>(
           (const B*)x, x_stride, (const B*)w, (const B*)bias, state, slots, cu_q, token_row, (B*)out, out_stride, C, taps, act, residual,
-          pure_decode);
+          pure_decode, slot_stride);
     } else
       causal_conv_kernel<B><<<grid, CONV_THREADS, 0, stream>>>((const B*)x, x_stride, (const B*)w, (const B*)bias, state, slots, cu_q,
-                                                                token_row, (B*)out, out_stride, C, taps, act, residual, pure_decode);
+                                                                token_row, (B*)out, out_stride, C, taps, act, residual, pure_decode, slot_stride);
     SB_LAUNCH_CHECK();
     if (!pure_decode && taps > 1)
-      conv_state_kernel<B><<<sgrid, CONV_THREADS, 0, stream>>>((const B*)x, x_stride, state, slots, cu_q, C, taps);
+      conv_state_kernel<B><<<sgrid, CONV_THREADS, 0, stream>>>((const B*)x, x_stride, state, slots, cu_q, C, taps, slot_stride);
   } else {
     return SB_ERR_DTYPE;
   }
@@ -540,7 +542,7 @@ SB_EXPORT int sb_linear_recurrence(int mode, const void* q, int q_stride, const 
                                    const void* aux, int aux_stride, const void* rate, int rate_stride, const float* decay,
                                    const void* a_log, const void* dt_bias, const void* d_skip, int par_dtype, float* state,
                                    const int* slots, const int* cu_q, float* out, int out_stride, int H, int Hqk, int dk, int dv,
-                                   float q_scale, int n_rows, int n_tokens, float* work, int dtype, cudaStream_t stream) {
+                                   float q_scale, int n_rows, int n_tokens, float* work, long long state_stride, int dtype, cudaStream_t stream) {
   if (n_rows <= 0 || n_tokens <= 0) return 0;
   if (!work || !aligned16(work)) return SB_ERR_ALIGN;
   if (H <= 0 || Hqk <= 0 || H % Hqk || dk <= 0 || dv <= 0) return SB_ERR_SHAPE;
@@ -548,7 +550,7 @@ SB_EXPORT int sb_linear_recurrence(int mode, const void* q, int q_stride, const 
   RecArgs a;
   a.q = q; a.k = k; a.v = v; a.q_stride = q_stride; a.k_stride = k_stride; a.v_stride = v_stride;
   a.aux = aux; a.aux_stride = aux_stride; a.rate = rate; a.rate_stride = rate_stride; a.decay = decay;
-  a.a_log = a_log; a.dt_bias = dt_bias; a.d_skip = d_skip; a.par_dtype = par_dtype; a.state = state; a.slots = slots; a.cu_q = cu_q;
+  a.a_log = a_log; a.dt_bias = dt_bias; a.d_skip = d_skip; a.par_dtype = par_dtype; a.state = state; a.state_stride = state_stride; a.slots = slots; a.cu_q = cu_q;
   a.out = out; a.out_stride = out_stride; a.H = H; a.Hqk = Hqk; a.dk = dk; a.dv = dv; a.P = 1; a.dkp = a.dvp = 0; a.n_tokens = n_tokens;
   a.q_scale = q_scale; a.qf = a.kf = a.af = a.vf = a.sc = a.dec = nullptr;
   if (dtype == SB_DTYPE_F32) {

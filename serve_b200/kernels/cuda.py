@@ -630,7 +630,8 @@ class CudaKernels:
         _check(self._seq_lib().sb_causal_conv(
             _p(x), x.stride(0), _p(weight), _p(bias), _p(state), _p(ctx.slots), _p(ctx.cu_q), _p(ctx.token_row), _p(out), out.stride(0),
             c, taps, {"none": 0, "silu": 1}[activation], 1 if residual else 0, x.shape[0], ctx.shape.rows,
-            1 if ctx.shape.pure_decode else 0, _DT[x.dtype], self._s()), "short convolution")
+            1 if ctx.shape.pure_decode else 0, ctypes.c_longlong(state.stride(0) if state is not None else 0), _DT[x.dtype], self._s()),
+            "short convolution")
 
     def linear_recurrence(self, mode: str, q, k, v, state, ctx, out, heads: int, qk_heads: int, dk: int, dv: int, aux=None, rate=None,
                           decay=None, a_log=None, dt_bias=None, d_skip=None, q_scale: float = 1.0) -> None:
@@ -652,7 +653,7 @@ class CudaKernels:
             _p(aux), aux.stride(0) if aux is not None else 0, _p(rate), rate.stride(0) if rate is not None else 0, _p(decay),
             _p(a_log), _p(dt_bias), _p(d_skip), _DT[par.dtype] if par is not None else 0, _p(state), _p(ctx.slots), _p(ctx.cu_q),
             _p(out), out.stride(0), heads, qk_heads, dk, dv, ctypes.c_float(q_scale), ctx.shape.rows, q.shape[0], _p(work),
-            _DT[v.dtype], self._s()),
+            ctypes.c_longlong(state.stride(0)), _DT[v.dtype], self._s()),
             "linear recurrence")
 
     def gated_norm(self, y, out, groups: int = 0, eps: float = 0.0, weight=None, gate=None, gate_act: str = "sigmoid",
