@@ -163,8 +163,9 @@ class CacheManager:
                     continue
                 if need.has_pages:
                     shape = (num_pages[self._entry_group[i]], need.kv_heads, page_size, need.head_dim)
-                    self._kv[i] = (torch.zeros(shape, dtype=kv_dtype, device=device),
-                                   torch.zeros(shape, dtype=kv_dtype, device=device))
+                    keys = torch.zeros(shape, dtype=kv_dtype, device=device)
+                    # a mixer whose values are its cached key rows gets the one tensor as both
+                    self._kv[i] = (keys, keys if need.shared_kv else torch.zeros(shape, dtype=kv_dtype, device=device))
                 if need.state_shape is not None:
                     self._state[i] = carve(need.state_shape)
                 for name, shape in need.states:
@@ -173,12 +174,12 @@ class CacheManager:
     # ---- sizes ----------------------------------------------------------
     @staticmethod
     def bytes_per_page(needs: Sequence[Optional[CacheNeed]], page_size: int, itemsize: int) -> List[int]:
-        """Per group: device bytes one page id costs across the group's executions (K and V)."""
+        """Per group: device bytes one page id costs across the group's executions (K and V, or the one tensor that is both)."""
         keys = CacheManager.group_keys(needs)
         out = [0] * len(keys)
         for n in needs:
             if n is not None and n.has_pages:
-                out[keys.index(n.group_key())] += 2 * page_size * n.kv_heads * n.head_dim * itemsize
+                out[keys.index(n.group_key())] += (1 if n.shared_kv else 2) * page_size * n.kv_heads * n.head_dim * itemsize
         return out
 
     @staticmethod

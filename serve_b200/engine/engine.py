@@ -59,6 +59,16 @@ class Engine:
         device = getattr(kernels, "device", None) or self.engine_config.device
         self.rt = Runtime(kernels, device, self.dtype)
         self.model = DecoderModel(self.spec, self.rt)
+        # the libraries the model's parts will call are compiled side by side now, not one after the other at first use
+        prepare = getattr(kernels, "prepare", None)
+        if prepare is not None:
+            dims, libs = set(), set()
+            for part in self.model.all_parts():
+                needs = part.kernel_needs()
+                dims.update(needs.get("attention_head_dims", ()))
+                libs.update(needs.get("libraries", ()))
+            if dims or libs:
+                prepare(sorted(dims), sorted(libs))
         self.cache: Optional[CacheManager] = None
         self.stepper: Optional[Stepper] = None
         self.max_context = min(self.engine_config.max_context or self.spec.max_position, self.spec.max_position)

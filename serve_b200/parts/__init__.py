@@ -5,3 +5,4 @@ from .base import (  # noqa: F401
 )
 from . import norm, rotary, attention, feed_forward, block, embedding  # noqa: F401
 from . import short_conv, gated_norm, linear_recurrence, biased_attention, parallel, routed_experts  # noqa: F401,E402
+from . import capped_attention, latent_attention  # noqa: F401,E402

@@ -45,6 +45,8 @@ class CacheNeed:
     ``state_shape`` (elements of float32 per request); a layer with several
     such states (a recurrence and the tails of its convolutions, say) names
     them in ``states``, a tuple of (name, shape) pairs. Any may be absent.
+    ``shared_kv``: the mixer's values are (a part of) its cached key rows, so the
+    cache keeps one tensor per execution and hands it out as both.
     """
 
     kv_heads: int = 0
@@ -53,6 +55,7 @@ class CacheNeed:
     state_shape: Optional[Tuple[int, ...]] = None
     chunk: Optional[int] = None
     states: Tuple[Tuple[str, Tuple[int, ...]], ...] = ()
+    shared_kv: bool = False      # keys and values are the same cached rows: one tensor serves as both
 
     @property
     def has_pages(self) -> bool:
@@ -60,7 +63,7 @@ class CacheNeed:
 
     def group_key(self) -> Tuple:
         """Executions with equal keys share page geometry, a pool and block tables."""
-        return (self.kv_heads, self.head_dim, self.window, self.chunk)
+        return (self.kv_heads, self.head_dim, self.window, self.chunk) + (("shared_kv",) if self.shared_kv else ())
 
     @staticmethod
     def merged(needs: "List[Tuple[str, Optional[CacheNeed]]]") -> "Optional[CacheNeed]":
@@ -79,7 +82,7 @@ class CacheNeed:
         if not paged and not states:
             return None
         p = paged[0] if paged else CacheNeed()
-        return CacheNeed(p.kv_heads, p.head_dim, p.window, None, p.chunk, tuple(states))
+        return CacheNeed(p.kv_heads, p.head_dim, p.window, None, p.chunk, tuple(states), p.shared_kv)
 
 
 class Part:
@@ -99,6 +102,12 @@ class Part:
 
     def load(self, tensors: Dict[str, Any]) -> None:
         """Take the declared tensors (already on the device, in their kept dtype)."""
+
+    def kernel_needs(self) -> Dict[str, Any]:
+        """Which compiled libraries this part will call: {"attention_head_dims": [...], "libraries": [names]}. The engine
+        builds what all parts of a model name side by side before the first step; a part that names nothing has its
+        libraries built when it first calls them."""
+        return {}
 
 
 class Mixer(Part):

@@ -14,13 +14,14 @@ from .base import Part, TensorDecl, register_part
 
 @register_part("embedding", "table")
 class TokenEmbedding(Part):
-    """params: vocab, hidden, name."""
+    """params: vocab, hidden, name, scale (every row is multiplied by it in float32; default 1)."""
 
     def __init__(self, spec, runtime):
         super().__init__(spec, runtime)
         self.vocab = int(spec.params["vocab"])
         self.hidden = int(spec.params["hidden"])
         self.name = self.prefix + spec.params.get("name", "weight")
+        self.scale = float(spec.params.get("scale") or 1.0)
         self.table = None
 
     def tensor_decls(self):
@@ -31,7 +32,10 @@ class TokenEmbedding(Part):
 
     def forward(self, tokens, ctx):
         x = torch.empty((tokens.shape[0], self.hidden), dtype=torch.float32, device=self.rt.device)
-        self.rt.kernels.embedding(tokens, self.table, x, getattr(ctx, "last_token", None))
+        if self.scale != 1.0:
+            self.rt.kernels.embedding(tokens, self.table, x, getattr(ctx, "last_token", None), scale=self.scale)
+        else:
+            self.rt.kernels.embedding(tokens, self.table, x, getattr(ctx, "last_token", None))
         return x
 
 

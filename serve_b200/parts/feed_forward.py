@@ -1,4 +1,4 @@
-"""Dense gated feed-forward (SwiGLU): down( silu(gate x) * (up x) ).
+"""Dense gated feed-forwards: down( act(gate x, up x) ), with act = silu(g) * u (SwiGLU) or a clamped form.
 
 Reference: serve/model.py:80-85 (w1 = gate, w3 = up, w2 = down, no biases).
 Gate and up weights are fused at load into one [2*I, hidden] matrix so that one
@@ -47,6 +47,36 @@ class SwiGLU(FeedForward):
         t = h.shape[0]
         act = rt.empty_act((t, self.intermediate))
         rt.kernels.gate_up_swiglu(h, self.w_gate_up, act)
+        out = rt.empty_act((t, self.hidden))
+        rt.kernels.linear(act, self.w_down, out)
+        return out
+
+
+@register_part("feed_forward", "gated_dense")
+class GatedDense(SwiGLU):
+    """The same three matrices with the activation as a parameter. params: hidden, intermediate, names, activation
+    ("swiglu" | "clamped_swish"), limit, alpha. clamped_swish: g <- min(g, limit), u <- clamp(u, -limit, limit),
+    g * sigmoid(alpha g) * (u + 1), computed in float32 on the float sums of the product where that is fused."""
+
+    def __init__(self, spec, runtime):
+        super().__init__(spec, runtime)
+        p = spec.params
+        self.activation = p.get("activation", "swiglu")
+        if self.activation not in ("swiglu", "clamped_swish"):
+            raise ValueError(f"gated_dense: activation {self.activation!r} is not known (swiglu, clamped_swish)")
+        self.limit = float(p.get("limit") or 0.0)
+        self.alpha = float(p.get("alpha") or 1.0)
+
+    def fused_description(self):
+        return None if self.activation != "swiglu" else super().fused_description()
+
+    def forward(self, h, ctx):
+        if self.activation == "swiglu":
+            return super().forward(h, ctx)
+        rt = self.rt
+        t = h.shape[0]
+        act = rt.empty_act((t, self.intermediate))
+        rt.kernels.gate_up_activation(h, self.w_gate_up, act, self.activation, self.limit, self.alpha)
         out = rt.empty_act((t, self.hidden))
         rt.kernels.linear(act, self.w_down, out)
         return out

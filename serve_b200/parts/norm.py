@@ -1,4 +1,4 @@
-"""RMS normalisation, fused with the residual addition that precedes it.
+"""RMS normalisation and layer normalisation, each fused with the residual addition that precedes it.
 
 Reference formula (serve/model.py:63-68): y = x32 * rsqrt(mean(x32^2) + eps),
 cast to the model dtype, times weight. Here the residual stream itself is kept
@@ -40,4 +40,23 @@ class RMSNorm(Norm):
     def forward_rows(self, x, delta, rows, ctx):
         out = self.rt.empty_act((rows.shape[0], self.size))
         self.rt.kernels.add_rmsnorm_rows(x, delta, rows, self.weight, self.eps, out)
+        return out
+
+
+@register_part("norm", "layer_norm")
+class LayerNorm(RMSNorm):
+    """y = (x - mean) / sqrt(var + eps) * weight, var the mean of the squared deviations, no bias; the same fusion with
+    the residual addition, in float32. params: size, eps, weight_name."""
+
+    def fused_description(self):
+        return None     # the kernel that runs whole layers knows RMS norms only
+
+    def forward(self, x, delta, ctx):
+        out = self.rt.empty_act((x.shape[0], self.size))
+        self.rt.kernels.add_layernorm(x, delta, self.weight, self.eps, out)
+        return out
+
+    def forward_rows(self, x, delta, rows, ctx):
+        out = self.rt.empty_act((rows.shape[0], self.size))
+        self.rt.kernels.add_layernorm_rows(x, delta, rows, self.weight, self.eps, out)
         return out

@@ -60,3 +60,50 @@ class RoutedExperts(FeedForward):
         rt.kernels.routed_experts(h, logits, self.w_gate_up, self.w_down, self.top, out, score=self.score, renormalise=self.renormalise,
                                   scale_input=self.scale_input, activation=self.activation, limit=self.limit, alpha=self.alpha)
         return out
+
+
+@register_part("feed_forward", "table_experts")
+class TableExperts(FeedForward):
+    """Experts without a router: an integer table [vocab, top] gives every token id its ``top`` experts (the entries
+    of a row differ), each weighing 1 / top on its output. An expert is down(act(up h)) without a gate; act is the
+    square of relu. The experts' matrices are stacked at load into [E, ff, hidden] and [E, hidden, ff]; grouping by
+    expert and the two products are those of the routed experts (csrc/routed_experts.cu).
+    params: hidden, experts, top, ff, vocab, activation ("relu_squared"), names: table, up, down (patterns with {e})."""
+
+    def __init__(self, spec, runtime):
+        super().__init__(spec, runtime)
+        p = spec.params
+        self.hidden, self.experts, self.top, self.ff = int(p["hidden"]), int(p["experts"]), int(p["top"]), int(p["ff"])
+        self.vocab = int(p["vocab"])
+        if not (1 <= self.top <= self.experts) or self.top > 16:
+            raise ValueError(f"top {self.top} of {self.experts} experts is not possible (at most 16 per token)")
+        self.activation = p.get("activation", "relu_squared")
+        if self.activation != "relu_squared":
+            raise ValueError(f"table_experts: activation {self.activation!r} is not known (relu_squared)")
+        names = dict(p.get("names", {}))
+        self.table_name = self.prefix + names.get("table", "table")
+        self.patterns = {k: self.prefix + names.get(k, "e{e}." + k) for k in ("up", "down")}
+        self.table = self.w_up = self.w_down = None
+
+    def kernel_needs(self):
+        return {"libraries": ["moe"]}
+
+    def tensor_decls(self):
+        decls = [TensorDecl(self.table_name, (self.vocab, self.top), role="table", init=f"choice:{self.experts}")]
+        for e in range(self.experts):
+            decls += [TensorDecl(self.patterns["up"].format(e=e), (self.ff, self.hidden)),
+                      TensorDecl(self.patterns["down"].format(e=e), (self.hidden, self.ff))]
+        return decls
+
+    def load(self, tensors):
+        self.table = tensors[self.table_name].contiguous()
+        if int(self.table.min()) < 0 or int(self.table.max()) >= self.experts:
+            raise ValueError(f"{self.table_name}: an entry names an expert outside 0..{self.experts - 1}")
+        self.w_up = torch.stack([tensors[self.patterns["up"].format(e=e)] for e in range(self.experts)]).contiguous()
+        self.w_down = torch.stack([tensors[self.patterns["down"].format(e=e)] for e in range(self.experts)]).contiguous()
+
+    def forward(self, h, ctx):
+        out = self.rt.empty_act((h.shape[0], self.hidden))
+        self.rt.kernels.table_experts(h, ctx.tokens, getattr(ctx, "last_token", None), self.table, self.w_up, self.w_down, self.top, out,
+                                      activation=self.activation)
+        return out

@@ -29,6 +29,11 @@ def random_tensor(decl: TensorDecl, seed: int, std: float = 0.02, norm_std: floa
     g = torch.Generator(device=device)
     g.manual_seed(_seed_for(seed, decl.name))
     if decl.role == "table":
+        if decl.init.startswith("choice:"):
+            # every row: distinct entries out of 0 .. n-1 (which experts a token id uses)
+            n = int(decl.init.split(":")[1])
+            order = torch.rand((decl.shape[0], n), generator=g, dtype=torch.float32, device=device).argsort(dim=1)
+            return order[:, : decl.shape[1]].to(torch.int32).contiguous()
         return torch.zeros(decl.shape, dtype=torch.int32, device=device)
     if decl.init == "norm":
         t = torch.ones(decl.shape, dtype=torch.float32, device=device)

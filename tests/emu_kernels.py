@@ -33,12 +33,32 @@ class EmuKernels:
     def fetch_ints(self, host, dev, n):
         dev.view(-1)[:n].copy_(host.view(-1)[:n])
 
-    def embedding(self, tokens, table, out, last_token=None):
+    @staticmethod
+    def _ids(tokens, last_token):
         ids = tokens.long()
         if last_token is not None:
             neg = ids < 0
             ids = torch.where(neg, last_token.long()[(-ids - 1).clamp(min=0)], ids)
-        out.copy_(table[ids].to(out.dtype))
+        return ids
+
+    def embedding(self, tokens, table, out, last_token=None, scale=1.0):
+        out.copy_((table[self._ids(tokens, last_token)].to(torch.float32) * scale).to(out.dtype))
+
+    def _layer_norm(self, v, weight, eps):
+        v = v.to(self.math)
+        d = v - v.mean(-1, keepdim=True)
+        return d * torch.rsqrt(d.pow(2).mean(-1, keepdim=True) + eps) * weight.to(self.math)
+
+    def add_layernorm(self, x, delta, weight, eps, out):
+        if delta is not None:
+            x.add_(delta.to(x.dtype))
+        out.copy_(self._layer_norm(x, weight, eps).to(out.dtype))
+
+    def add_layernorm_rows(self, x, delta, rows, weight, eps, out):
+        v = x[rows.long()]
+        if delta is not None:
+            v = v + delta[rows.long()].to(x.dtype)
+        out.copy_(self._layer_norm(v, weight, eps).to(out.dtype))
 
     def _norm(self, v, weight, eps):
         v = v.to(self.math)
@@ -100,8 +120,81 @@ class EmuKernels:
             k_cache[pages, :, pos % page_size] = qk[:, heads:]          # caches are [pages, kv_heads, page_size, D]
             v_cache[pages, :, pos % page_size] = x[:, heads + kv_heads:]
 
+    def gate_up_activation(self, h, w_gate_up, out, activation, limit=0.0, alpha=1.0):
+        gate_up = torch.empty((h.shape[0], w_gate_up.shape[0]), dtype=h.dtype, device=h.device)
+        self.linear(h, w_gate_up, gate_up)
+        inter = out.shape[1]
+        g, u = gate_up[:, :inter].to(self.math), gate_up[:, inter:].to(self.math)
+        if activation == "clamped_swish":
+            g, u = torch.clamp(g, max=limit), torch.clamp(u, -limit, limit)
+            out.copy_((g * torch.sigmoid(alpha * g) * (u + 1)).to(out.dtype))
+        else:
+            out.copy_((g * torch.sigmoid(g) * u).to(out.dtype))
+
+    def linear_batched(self, a, w, out):
+        """out[:, b] = a[:, b] @ w[b]^T for every b: a [M, B, K], w [B, N, K], out [M, B, N] (views with any row strides)."""
+        out.copy_(torch.einsum("mbk,bnk->mbn", a.to(self.math), w.to(self.math)).to(out.dtype))
+
+    def _write_pages(self, cache, rows, positions, token_row, block_table, page_size):
+        pos = positions.long()
+        pages = block_table.long()[token_row.long(), pos // page_size]
+        assert bool((pages >= 0).all()), "cache write to a missing page"
+        cache[pages, :, pos % page_size] = rows.to(cache.dtype)
+
+    def normed_qk_cache_write(self, proj, positions, token_row, heads, kv_heads, head_dim, dim, q_weight, k_weight, eps, temp_coef,
+                              temp_every, k_cache, v_cache, block_table, page_size, write_cache):
+        t, d, m = proj.shape[0], head_dim, self.math
+        x = proj.view(t, heads + 2 * kv_heads, d)
+        q, k = x[:, :heads].to(m).reshape(t, heads * d), x[:, heads: heads + kv_heads].to(m).reshape(t, kv_heads * d)
+        if q_weight is not None:
+            q = q * torch.rsqrt(q.pow(2).sum(-1, keepdim=True) / (heads * dim) + eps) * q_weight.to(m)
+            k = k * torch.rsqrt(k.pow(2).sum(-1, keepdim=True) / (kv_heads * dim) + eps) * k_weight.to(m)
+        if temp_coef:
+            temp = 1.0 + temp_coef * torch.log((torch.div(positions.long() + 1, temp_every, rounding_mode="floor") + 1).to(torch.float32))
+            q = q * temp.to(m)[:, None]
+        x[:, :heads] = q.view(t, heads, d).to(proj.dtype)
+        if write_cache:
+            self._write_pages(k_cache, k.view(t, kv_heads, d), positions, token_row, block_table, page_size)
+            self._write_pages(v_cache, x[:, heads + kv_heads:], positions, token_row, block_table, page_size)
+
+    def latent_prepare(self, proj, n_q, positions, token_row, c_weight, eps, inv_freq, rot_dims, heads, dim, rot_dim, rank, head_dim,
+                       q_lat, k_cache, block_table, page_size, write_cache):
+        t, m = proj.shape[0], self.math
+        ang = positions.to(torch.float32)[:, None] * inv_freq.to(torch.float32)[None, :]
+        cos, sin = ang.cos().to(m), ang.sin().to(m)
+
+        def rotate(v):                      # [..., rot_dim] with t leading
+            a, b = v[..., 0:rot_dims:2], v[..., 1:rot_dims:2]
+            shape = (t,) + (1,) * (v.dim() - 2) + (rot_dims // 2,)
+            c, s = cos.view(shape), sin.view(shape)
+            return torch.cat([torch.stack([a * c - b * s, b * c + a * s], -1).flatten(-2), v[..., rot_dims:]], -1)
+
+        q = proj[:, :n_q].view(t, heads, dim + rot_dim).to(m)
+        ql = q_lat.view(t, heads, head_dim)
+        ql[:, :, rank: rank + rot_dim] = rotate(q[..., dim:]).to(q_lat.dtype)
+        ql[:, :, rank + rot_dim:] = 0
+        down = proj[:, n_q: n_q + rank + rot_dim].to(m)
+        c = down[:, :rank]
+        c = c * torch.rsqrt(c.pow(2).mean(-1, keepdim=True) + eps) * c_weight.to(m)
+        if write_cache:
+            row = torch.zeros((t, 1, head_dim), dtype=m, device=proj.device)
+            row[:, 0, :rank] = c
+            row[:, 0, rank: rank + rot_dim] = rotate(down[:, rank:])
+            self._write_pages(k_cache, row, positions, token_row, block_table, page_size)
+
+    def table_experts(self, h, tokens, last_token, table, w_up, w_down, top, out, activation="relu_squared"):
+        m = self.math
+        idx = table.long()[self._ids(tokens, last_token)]            # [T, top]
+        total = torch.zeros((h.shape[0], w_down.shape[1]), dtype=m, device=h.device)
+        for slot in range(top):
+            for e in idx[:, slot].unique().tolist():
+                rows = (idx[:, slot] == e).nonzero().flatten()
+                a = torch.relu(h[rows].to(m) @ w_up[e].to(m).T) ** 2
+                total[rows] += (a.to(h.dtype).to(m) @ w_down[e].to(m).T) / top
+        out.copy_(total.to(out.dtype))
+
     def attention(self, qkv, k_cache, v_cache, block_table, cu_q, kv_len, token_row, positions, heads, kv_heads, head_dim,
-                  page_size, scale, window, out, shape, slopes=None, chunk=0):
+                  page_size, scale, window, out, shape, slopes=None, chunk=0, softcap=0.0, sinks=None):
         d = head_dim
         g = heads // kv_heads
         cu = cu_q.tolist()
@@ -122,6 +215,8 @@ class EmuKernels:
             v = v_cache[pages, :, key_pos[lo:] % page_size].to(self.math)
             kk, vv = k.repeat_interleave(g, 1), v.repeat_interleave(g, 1)
             s = torch.einsum("thd,shd->hts", q, kk) * scale
+            if softcap:
+                s = softcap * torch.tanh(s / softcap)       # before any distance bias
             qp = torch.arange(L - n, L, device=qkv.device)[:, None]
             kp = key_pos[lo:][None, :]
             mask = kp > qp
@@ -132,7 +227,12 @@ class EmuKernels:
             if slopes is not None:
                 s = s - slopes.to(self.math)[:, None, None] * (qp - kp).to(self.math)[None]
             s = s.masked_fill(mask[None], float("-inf"))
-            o = torch.einsum("hts,shd->thd", torch.softmax(s, -1), vv)
+            if sinks is not None:
+                # the sink is one more score without a value: a column that the product with the values leaves out
+                s = torch.cat([s, sinks.to(self.math)[:, None, None].expand(heads, n, 1)], -1)
+                o = torch.einsum("hts,shd->thd", torch.softmax(s, -1)[..., :-1], vv)
+            else:
+                o = torch.einsum("hts,shd->thd", torch.softmax(s, -1), vv)
             out[q0:q1] = o.reshape(n, heads * d).to(out.dtype)
 
     # ---- mixers with recurrent state, routed experts -------------------------------------------------------------
