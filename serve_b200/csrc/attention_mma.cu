@@ -73,6 +73,9 @@ struct Params {
   float scale_log2; int window;
   const float* slopes;   // one per query head, or null: slope * (position - key) is taken off a score (in the score's own units)
   int chunk;             // > 0: a query sees only the keys from floor(position / chunk) * chunk on
+  float softcap_log2;    // > 0: a scaled score s becomes c * tanh(s / c), c the cap (kept here times log2 e), before any bias
+  float softcap_in;      // scale / c: what the raw product is multiplied by inside the tanh
+  const float* sinks;    // one per query head, or null: exp(sink) joins the softmax's denominator (no key, no value), once per row
   bf16* out;
   // deep shape only
   int split_size, num_splits;
@@ -121,6 +124,11 @@ __device__ __forceinline__ void merge_splits(const Params& p, int r, int hk, int
     float mm = -INFINITY;
     for (int s_ = 0; s_ < S; ++s_) mm = fmaxf(mm, f_s[s_][row]);
     float ll = 0.f;
+    if (p.sinks != nullptr && row < M) {
+      const float sk = p.sinks[hk * p.G + row % p.G] * LOG2E;
+      mm = fmaxf(mm, sk);
+      ll = exp2f(sk - mm);
+    }
     for (int s_ = 0; s_ < S; ++s_) {
       const float ms = f_s[s_][row];
       const float f = (ms == -INFINITY) ? 0.f : exp2f(ms - mm);
@@ -230,7 +238,8 @@ __global__ void __launch_bounds__(THREADS, (D <= 64 ? 4 : 1)) attention_wide_ker
   const int hi = p0 + row_last / G + 1;             // exclusive, <= L
   // keys every row of the tile may see without a mask (none with a distance bias or blocks of positions: every score
   // then goes through the masked path, which also takes the bias off)
-  const bool by_distance = p.slopes != nullptr || p.chunk > 0;
+  const bool capped = p.softcap_log2 > 0.f;
+  const bool by_distance = p.slopes != nullptr || p.chunk > 0 || capped;     // every score takes the masked path
   const int free_lo = by_distance ? 0x7fffffff : (p.window > 0 ? max(lo, p0 + row_last / G - p.window + 1) : lo);
   const int free_hi = by_distance ? 0 : min(hi, p0 + tok_first + 1);
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -326,8 +335,10 @@ __global__ void __launch_bounds__(THREADS, (D <= 64 ? 4 : 1)) attention_wide_ker
           const bool in_range = key >= lo && key < hi;
           const bool ok_a = in_range && key <= pos_a && key >= first_a && (p.window <= 0 || key > pos_a - p.window);
           const bool ok_b = in_range && key <= pos_b && key >= first_b && (p.window <= 0 || key > pos_b - p.window);
-          s[j][e] = ok_a ? s[j][e] * p.scale_log2 - slope_a * (float)(pos_a - key) : -INFINITY;
-          s[j][2 + e] = ok_b ? s[j][2 + e] * p.scale_log2 - slope_b * (float)(pos_b - key) : -INFINITY;
+          const float va = capped ? p.softcap_log2 * tanhf(s[j][e] * p.softcap_in) : s[j][e] * p.scale_log2;
+          const float vb = capped ? p.softcap_log2 * tanhf(s[j][2 + e] * p.softcap_in) : s[j][2 + e] * p.scale_log2;
+          s[j][e] = ok_a ? va - slope_a * (float)(pos_a - key) : -INFINITY;
+          s[j][2 + e] = ok_b ? vb - slope_b * (float)(pos_b - key) : -INFINITY;
           mx_a = fmaxf(mx_a, s[j][e]);
           mx_b = fmaxf(mx_b, s[j][2 + e]);
         }
@@ -376,7 +387,20 @@ __global__ void __launch_bounds__(THREADS, (D <= 64 ? 4 : 1)) attention_wide_ker
   l_a += __shfl_xor_sync(0xffffffffu, l_a, 2);
   l_b += __shfl_xor_sync(0xffffffffu, l_b, 1);
   l_b += __shfl_xor_sync(0xffffffffu, l_b, 2);
-  const float inv_a = l_a > 0.f ? 1.f / l_a : 0.f, inv_b = l_b > 0.f ? 1.f / l_b : 0.f;
+  float fin_a = 1.f, fin_b = 1.f;          // what the accumulated outputs are scaled by once the sink has joined the sum
+  if (p.sinks != nullptr) {
+    if (row_a < M) {
+      const float sk = p.sinks[hk * G + row_a % G] * LOG2E, mn = fmaxf(m_a, sk);
+      fin_a = (m_a == -INFINITY) ? 0.f : exp2f(m_a - mn);
+      l_a = l_a * fin_a + exp2f(sk - mn);
+    }
+    if (row_b < M) {
+      const float sk = p.sinks[hk * G + row_b % G] * LOG2E, mn = fmaxf(m_b, sk);
+      fin_b = (m_b == -INFINITY) ? 0.f : exp2f(m_b - mn);
+      l_b = l_b * fin_b + exp2f(sk - mn);
+    }
+  }
+  const float inv_a = l_a > 0.f ? fin_a / l_a : 0.f, inv_b = l_b > 0.f ? fin_b / l_b : 0.f;
   if (row_a < M) {
     const int tok = row_a / G, hd = hk * G + (row_a - tok * G);
     bf16* dst = p.out + (size_t)(q0 + tok) * p.H * D + (size_t)hd * D + tq * 2;
@@ -565,7 +589,8 @@ __global__ void __launch_bounds__(NWARPS * 32) attention_deep_kernel(const Param
   const int first_b = (p.chunk > 0 && pos_b >= 0) ? (pos_b / p.chunk) * p.chunk : 0;
   // a sub-tile all of whose keys every row may see needs no mask: keys in [free_lo, free_hi) (none with a distance
   // bias or blocks of positions: the masked path takes the bias off)
-  const bool by_distance = p.slopes != nullptr || p.chunk > 0;
+  const bool capped = p.softcap_log2 > 0.f;
+  const bool by_distance = p.slopes != nullptr || p.chunk > 0 || capped;     // every score takes the masked path
   const int free_lo = by_distance ? 0x7fffffff : max(lo, p.window > 0 ? p0 + (M - 1) / G - p.window + 1 : 0);
   const int free_hi = by_distance ? 0 : min(hi, p0 + 1);
   float o[D / 8][4];
@@ -627,11 +652,13 @@ __global__ void __launch_bounds__(NWARPS * 32) attention_deep_kernel(const Param
           const int key = kbase + j * 8 + tq * 2 + e;
           const bool in_range = key >= lo && key < hi;
           const bool ok_a = in_range && key <= pos_a && key >= first_a && (p.window <= 0 || key > pos_a - p.window);
-          s[j][e] = ok_a ? s[j][e] * p.scale_log2 - slope_a * (float)(pos_a - key) : -INFINITY;
+          const float va = capped ? p.softcap_log2 * tanhf(s[j][e] * p.softcap_in) : s[j][e] * p.scale_log2;
+          s[j][e] = ok_a ? va - slope_a * (float)(pos_a - key) : -INFINITY;
           mx_a = fmaxf(mx_a, s[j][e]);
           if (UPPER) {
             const bool ok_b = in_range && key <= pos_b && key >= first_b && (p.window <= 0 || key > pos_b - p.window);
-            s[j][2 + e] = ok_b ? s[j][2 + e] * p.scale_log2 - slope_b * (float)(pos_b - key) : -INFINITY;
+            const float vb = capped ? p.softcap_log2 * tanhf(s[j][2 + e] * p.softcap_in) : s[j][2 + e] * p.scale_log2;
+            s[j][2 + e] = ok_b ? vb - slope_b * (float)(pos_b - key) : -INFINITY;
             mx_b = fmaxf(mx_b, s[j][2 + e]);
           }
         }
@@ -725,6 +752,12 @@ __global__ void __launch_bounds__(NWARPS * 32) attention_deep_kernel(const Param
       ll += MLm[(w * 16 + row) * 2 + 1] * f;
       acc += Om[((size_t)w * 16 + row) * D + d] * f;
     }
+    if (last && p.sinks != nullptr) {
+      const float sk = p.sinks[hk * G + row % G] * LOG2E, mn = fmaxf(mm, sk);
+      const float f = (mm == -INFINITY) ? 0.f : exp2f(mm - mn);
+      ll = ll * f + exp2f(sk - mn);
+      acc *= f;
+    }
     if (last) {
       const int tok = row / G, hd = hk * G + (row - tok * G);
       p.out[(size_t)(q0 + tok) * p.H * D + (size_t)hd * D + d] = __float2bfloat16_rn(ll > 0.f ? acc / ll : 0.f);
@@ -778,11 +811,12 @@ SB_EXPORT long long sb_attention_mma_scratch_bytes(int n_rows, int Hkv, int num_
 // ``scratch`` (sb_attention_mma_scratch_bytes) and merges either in the block that finishes last (tickets: n_rows * Hkv
 // ints, zero before the first launch; every launch leaves them zero) or, with tickets == nullptr, in a second kernel.
 // ``slopes`` (float [H] or null) and ``chunk`` (0: none): scores that depend on distance, see Params.
-SB_EXPORT int sb_attention_mma_biased(const void* qkv, int q_stride, const void* kc, const void* vc, const int* block_table, int bt_width,
-                                      const int* cu_q, const int* kv_len, int H, int Hkv, int ps, int num_pages, float scale, int window,
-                                      void* out, int n_rows, int max_q, int which, int longest, int num_splits, void* scratch,
-                                      int* tickets, const int* wide_rows, int n_wide, const float* slopes, int chunk,
-                                      cudaStream_t stream) {
+// ``softcap`` (0: none) and ``sinks`` (float [H] or null): see Params.
+SB_EXPORT int sb_attention_mma_opts(const void* qkv, int q_stride, const void* kc, const void* vc, const int* block_table, int bt_width,
+                                    const int* cu_q, const int* kv_len, int H, int Hkv, int ps, int num_pages, float scale, int window,
+                                    void* out, int n_rows, int max_q, int which, int longest, int num_splits, void* scratch,
+                                    int* tickets, const int* wide_rows, int n_wide, const float* slopes, int chunk, float softcap,
+                                    const float* sinks, cudaStream_t stream) {
   if (n_rows <= 0 || max_q <= 0) return 0;
   if (H <= 0 || Hkv <= 0 || H % Hkv || ps <= 0 || bt_width <= 0) return SB_ERR_SHAPE;
   if (Hkv > 65535 || n_rows > 65535) return SB_ERR_LIMIT;
@@ -793,6 +827,7 @@ SB_EXPORT int sb_attention_mma_biased(const void* qkv, int q_stride, const void*
   p.H = H; p.Hkv = Hkv; p.G = H / Hkv; p.ps = ps; p.num_pages = num_pages;
   p.ps_shift = (ps & (ps - 1)) == 0 ? __builtin_ctz((unsigned)ps) : -1;
   p.scale_log2 = scale * LOG2E; p.window = window; p.out = (bf16*)out; p.slopes = slopes; p.chunk = chunk;
+  p.softcap_log2 = softcap > 0.f ? softcap * LOG2E : 0.f; p.softcap_in = softcap > 0.f ? scale / softcap : 0.f; p.sinks = sinks;
   p.split_size = 0; p.num_splits = num_splits; p.part_o = nullptr; p.part_ml = nullptr; p.tickets = nullptr;
   p.wide_rows = wide_rows; p.heads_in_x = 0;
   if (which & 1) {
@@ -879,6 +914,16 @@ constexpr int kNoallocMaxDevices = 64;
 void* g_noalloc_addr[kNoallocMaxDevices];
 }  // namespace
 
+SB_EXPORT int sb_attention_mma_biased(const void* qkv, int q_stride, const void* kc, const void* vc, const int* block_table, int bt_width,
+                                      const int* cu_q, const int* kv_len, int H, int Hkv, int ps, int num_pages, float scale, int window,
+                                      void* out, int n_rows, int max_q, int which, int longest, int num_splits, void* scratch,
+                                      int* tickets, const int* wide_rows, int n_wide, const float* slopes, int chunk,
+                                      cudaStream_t stream) {
+  return sb_attention_mma_opts(qkv, q_stride, kc, vc, block_table, bt_width, cu_q, kv_len, H, Hkv, ps, num_pages, scale, window, out,
+                               n_rows, max_q, which, longest, num_splits, scratch, tickets, wide_rows, n_wide, slopes, chunk, 0.f, nullptr,
+                               stream);
+}
+
 SB_EXPORT int sb_attention_mma(const void* qkv, int q_stride, const void* kc, const void* vc, const int* block_table, int bt_width,
                                const int* cu_q, const int* kv_len, int H, int Hkv, int ps, int num_pages, float scale, int window,
                                void* out, int n_rows, int max_q, int which, int longest, int num_splits, void* scratch,
@@ -922,6 +967,7 @@ SB_EXPORT int sb_attention_decode_noalloc(const void* qkv, int q_stride, const v
   p.H = H; p.Hkv = Hkv; p.G = G; p.ps = ps; p.num_pages = num_pages;
   p.ps_shift = (ps & (ps - 1)) == 0 ? __builtin_ctz((unsigned)ps) : -1;
   p.scale_log2 = scale * LOG2E; p.window = window; p.out = (bf16*)out; p.slopes = nullptr; p.chunk = 0;
+  p.softcap_log2 = 0.f; p.softcap_in = 0.f; p.sinks = nullptr;
   p.split_size = 0; p.num_splits = num_splits; p.part_o = nullptr; p.part_ml = nullptr; p.tickets = nullptr;
   p.wide_rows = nullptr;
   if (num_splits > 1) {

@@ -9,6 +9,9 @@
 // head, or null) takes slope_h * (p - key) off every score, and ``chunk`` > 0
 // hides the keys before floor(p / chunk) * chunk (positions count from the start
 // of the sequence, so the blocks do not move with how a prompt was cut).
+// Two more: ``softcap`` c > 0 turns a scaled score s into c * tanh(s / c) (before any distance bias), and ``sinks``
+// (one float per query head, or null) adds exp(sink_h) to the softmax's denominator: a score without key or value,
+// neither scaled nor capped, counted once per row however the keys are split.
 // Scores, running maximum, sum and the output accumulator are float; the
 // online-softmax recurrences are those of serve/kernels/attn_prefill.py:58-72,
 // in base e. Compile with -DSB_HEAD_DIM=<multiple of 16>.
@@ -35,7 +38,7 @@ __global__ void __launch_bounds__(THREADS) attention_simt_kernel(
     const T* __restrict__ qkv, int q_stride, const T* __restrict__ kc, const T* __restrict__ vc,  // caches [P, Hkv, ps, D]
     const int* __restrict__ block_table, int bt_width, const int* __restrict__ cu_q, const int* __restrict__ kv_len, int H,
     int Hkv, int ps, int num_pages, float scale, int window, T* __restrict__ out, int decode_apart,
-    const float* __restrict__ slopes, int chunk) {
+    const float* __restrict__ slopes, int chunk, float softcap, const float* __restrict__ sinks) {
   extern __shared__ float smem[];
   float* Qs = smem;                 // [BM][D]
   float* Ks = Qs + BM * D;          // [BN][KSTRIDE]
@@ -106,7 +109,9 @@ __global__ void __launch_bounds__(THREADS) attention_simt_kernel(
     for (int c = 0; c < BN / 8; ++c) {
       const int key = kt + jj + 8 * c;
       const bool ok = row_ok && key <= pi && key >= chunk_lo && (window <= 0 || key > pi - window);
-      s[c] = ok ? s[c] * scale - slope * (float)(pi - key) : -INFINITY;
+      float sv = s[c] * scale;
+      if (softcap > 0.f) sv = softcap * tanhf(sv / softcap);
+      s[c] = ok ? sv - slope * (float)(pi - key) : -INFINITY;
       tmax = fmaxf(tmax, s[c]);
     }
     tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, 1));
@@ -136,6 +141,14 @@ __global__ void __launch_bounds__(THREADS) attention_simt_kernel(
     }
   }
   if (row_ok) {
+    if (sinks != nullptr) {
+      const float sk = sinks[h];
+      const float m_fin = fmaxf(m_run, sk);
+      const float a = (m_run == -INFINITY) ? 0.f : expf(m_run - m_fin);
+      l_run = l_run * a + expf(sk - m_fin);
+#pragma unroll
+      for (int c = 0; c < D / 8; ++c) acc[c] *= a;
+    }
     const float inv = l_run > 0.f ? 1.0f / l_run : 0.f;
     T* orow = out + (size_t)(q0 + m0 + i) * H * D + (size_t)h * D;
 #pragma unroll
@@ -186,7 +199,8 @@ template <typename T>
 __global__ void __launch_bounds__(DEC_WARPS * 32) attention_simt_decode_kernel(
     const T* __restrict__ qkv, int q_stride, const T* __restrict__ kc, const T* __restrict__ vc,
     const int* __restrict__ block_table, int bt_width, const int* __restrict__ cu_q, const int* __restrict__ kv_len, int H,
-    int Hkv, int ps, int num_pages, float scale, int window, T* __restrict__ out, const float* __restrict__ slopes, int chunk) {
+    int Hkv, int ps, int num_pages, float scale, int window, T* __restrict__ out, const float* __restrict__ slopes, int chunk,
+    float softcap, const float* __restrict__ sinks) {
   extern __shared__ float smem[];
   float* Qs = smem;                                        // [16][D]
   float* Om = Qs + 16 * D;                                 // [DEC_STREAMS][DEC_ROWS][LPK * EPL]
@@ -264,6 +278,7 @@ __global__ void __launch_bounds__(DEC_WARPS * 32) attention_simt_decode_kernel(
         for (int o = LPK / 2; o > 0; o >>= 1) sc += __shfl_xor_sync(0xffffffffu, sc, o);
         const bool ok = this_there && this_key <= pos[i] && this_key >= first_key[i] && (window <= 0 || this_key > pos[i] - window);
         if (ok) {
+          if (softcap > 0.f) sc = softcap * tanhf(sc / softcap);
           sc -= slope[i] * (float)(pos[i] - this_key);
           const float m_new = fmaxf(m_run[i], sc);
           const float alpha = (m_run[i] == -INFINITY) ? 0.f : expf(m_run[i] - m_new);
@@ -288,6 +303,11 @@ __global__ void __launch_bounds__(DEC_WARPS * 32) attention_simt_decode_kernel(
       float mm = -INFINITY;
       for (int st = 0; st < DEC_STREAMS; ++st) mm = fmaxf(mm, MLm[(st * DEC_ROWS + i) * 2]);
       float ll = 0.f, o = 0.f;
+      if (sinks != nullptr) {
+        const float sk = sinks[hk * G + (m0 + i) % G];
+        mm = fmaxf(mm, sk);
+        ll = expf(sk - mm);
+      }
       for (int st = 0; st < DEC_STREAMS; ++st) {
         const float mw = MLm[(st * DEC_ROWS + i) * 2];
         const float f = (mw == -INFINITY) ? 0.f : expf(mw - mm);
@@ -305,12 +325,12 @@ __global__ void __launch_bounds__(DEC_WARPS * 32) attention_simt_decode_kernel(
 
 SB_EXPORT int sb_attention_simt_head_dim() { return D; }
 
-// As sb_attention_simt below, with the two options of scores that depend on distance: ``slopes`` (float [H] or null)
-// and ``chunk`` (0: none).
-SB_EXPORT int sb_attention_simt_biased(const void* qkv, int q_stride, const void* kc, const void* vc, const int* block_table,
-                                       int bt_width, const int* cu_q, const int* kv_len, int H, int Hkv, int ps, int num_pages,
-                                       float scale, int window, void* out, int n_rows, int max_q, int dtype, const float* slopes,
-                                       int chunk, cudaStream_t stream) {
+// As sb_attention_simt below, with every option: ``slopes`` (float [H] or null), ``chunk`` (0: none), ``softcap`` (0: none)
+// and ``sinks`` (float [H] or null).
+SB_EXPORT int sb_attention_simt_opts(const void* qkv, int q_stride, const void* kc, const void* vc, const int* block_table,
+                                     int bt_width, const int* cu_q, const int* kv_len, int H, int Hkv, int ps, int num_pages,
+                                     float scale, int window, void* out, int n_rows, int max_q, int dtype, const float* slopes,
+                                     int chunk, float softcap, const float* sinks, cudaStream_t stream) {
   if (n_rows <= 0 || max_q <= 0) return 0;
   if (H <= 0 || Hkv <= 0 || H % Hkv || ps <= 0 || bt_width <= 0) return SB_ERR_SHAPE;
   if (H > 65535 || n_rows > 65535) return SB_ERR_LIMIT;
@@ -328,7 +348,7 @@ SB_EXPORT int sb_attention_simt_biased(const void* qkv, int q_stride, const void
       auto k = attention_simt_kernel<float>;
       if (smem > 48 * 1024) cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
       k<<<grid, THREADS, smem, stream>>>((const float*)qkv, q_stride, (const float*)kc, (const float*)vc, block_table, bt_width, cu_q,
-                                         kv_len, H, Hkv, ps, num_pages, scale, window, (float*)out, decode_shape ? 1 : 0, slopes, chunk);
+                                         kv_len, H, Hkv, ps, num_pages, scale, window, (float*)out, decode_shape ? 1 : 0, slopes, chunk, softcap, sinks);
       SB_LAUNCH_CHECK();
     }
     if (decode_shape) {
@@ -338,14 +358,14 @@ SB_EXPORT int sb_attention_simt_biased(const void* qkv, int q_stride, const void
     if (decode_shape)
       attention_simt_decode_kernel<float><<<dgrid, DEC_WARPS * 32, dsmem, stream>>>(
           (const float*)qkv, q_stride, (const float*)kc, (const float*)vc, block_table, bt_width, cu_q, kv_len, H, Hkv, ps, num_pages,
-          scale, window, (float*)out, slopes, chunk);
+          scale, window, (float*)out, slopes, chunk, softcap, sinks);
   } else if (dtype == SB_DTYPE_BF16) {
     if (tiles_needed) {
       auto k = attention_simt_kernel<__nv_bfloat16>;
       if (smem > 48 * 1024) cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
       k<<<grid, THREADS, smem, stream>>>((const __nv_bfloat16*)qkv, q_stride, (const __nv_bfloat16*)kc, (const __nv_bfloat16*)vc,
                                          block_table, bt_width, cu_q, kv_len, H, Hkv, ps, num_pages, scale, window,
-                                         (__nv_bfloat16*)out, decode_shape ? 1 : 0, slopes, chunk);
+                                         (__nv_bfloat16*)out, decode_shape ? 1 : 0, slopes, chunk, softcap, sinks);
       SB_LAUNCH_CHECK();
     }
     if (decode_shape) {
@@ -355,12 +375,21 @@ SB_EXPORT int sb_attention_simt_biased(const void* qkv, int q_stride, const void
     if (decode_shape)
       attention_simt_decode_kernel<__nv_bfloat16><<<dgrid, DEC_WARPS * 32, dsmem, stream>>>(
           (const __nv_bfloat16*)qkv, q_stride, (const __nv_bfloat16*)kc, (const __nv_bfloat16*)vc, block_table, bt_width, cu_q, kv_len, H,
-          Hkv, ps, num_pages, scale, window, (__nv_bfloat16*)out, slopes, chunk);
+          Hkv, ps, num_pages, scale, window, (__nv_bfloat16*)out, slopes, chunk, softcap, sinks);
   } else {
     return SB_ERR_DTYPE;
   }
   SB_LAUNCH_CHECK();
   return 0;
+}
+
+// The two options of scores that depend on distance only.
+SB_EXPORT int sb_attention_simt_biased(const void* qkv, int q_stride, const void* kc, const void* vc, const int* block_table,
+                                       int bt_width, const int* cu_q, const int* kv_len, int H, int Hkv, int ps, int num_pages,
+                                       float scale, int window, void* out, int n_rows, int max_q, int dtype, const float* slopes,
+                                       int chunk, cudaStream_t stream) {
+  return sb_attention_simt_opts(qkv, q_stride, kc, vc, block_table, bt_width, cu_q, kv_len, H, Hkv, ps, num_pages, scale, window, out,
+                                n_rows, max_q, dtype, slopes, chunk, 0.f, nullptr, stream);
 }
 
 SB_EXPORT int sb_attention_simt(const void* qkv, int q_stride, const void* kc, const void* vc, const int* block_table, int bt_width,

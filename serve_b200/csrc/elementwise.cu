@@ -14,7 +14,7 @@ using namespace sb;
 // seen the previous step's tokens.
 template <typename T>
 __global__ void embedding_kernel(const int* __restrict__ tokens, const T* __restrict__ table, float* __restrict__ out,
-                                 int dim, int vocab, const int* __restrict__ last_token, int n_slots) {
+                                 int dim, int vocab, const int* __restrict__ last_token, int n_slots, float scale) {
   const int t = blockIdx.x;
   pdl_launch_dependents();
   pdl_wait();
@@ -23,7 +23,7 @@ __global__ void embedding_kernel(const int* __restrict__ tokens, const T* __rest
   const bool ok = tok >= 0 && tok < vocab;
   const T* src = table + (size_t)(ok ? tok : 0) * dim;
   float* dst = out + (size_t)t * dim;
-  for (int i = threadIdx.x; i < dim; i += blockDim.x) dst[i] = ok ? to_float(src[i]) : 0.f;
+  for (int i = threadIdx.x; i < dim; i += blockDim.x) dst[i] = ok ? to_float(src[i]) * scale : 0.f;
 }
 
 // A step's packed integer inputs, from pinned host memory to the device buffer the kernels read, copied by a kernel:
@@ -44,17 +44,18 @@ SB_EXPORT int sb_fetch_ints(const int* src, int* dst, int n, cudaStream_t stream
   return 0;
 }
 
+// out[t] = table[token] * scale (the product in float; scale 1 leaves the row as stored).
 SB_EXPORT int sb_embedding(const int* tokens, const void* table, float* out, int n_tokens, int dim, int vocab, int dtype,
-                           const int* last_token, int n_slots, cudaStream_t stream) {
+                           const int* last_token, int n_slots, float scale, cudaStream_t stream) {
   if (n_tokens <= 0) return 0;
   if (dim <= 0 || vocab <= 0) return SB_ERR_SHAPE;
   const int threads = dim >= 1024 ? 256 : 128;
   if (dtype == SB_DTYPE_F32)
     SB_PDL_CHECK(launch_pdl(embedding_kernel<float>, dim3(n_tokens), dim3(threads), 0, stream, tokens, (const float*)table, out, dim, vocab,
-                            last_token, n_slots));
+                            last_token, n_slots, scale));
   else if (dtype == SB_DTYPE_BF16)
     SB_PDL_CHECK(launch_pdl(embedding_kernel<__nv_bfloat16>, dim3(n_tokens), dim3(threads), 0, stream, tokens,
-                            (const __nv_bfloat16*)table, out, dim, vocab, last_token, n_slots));
+                            (const __nv_bfloat16*)table, out, dim, vocab, last_token, n_slots, scale));
   else
     return SB_ERR_DTYPE;
   return 0;

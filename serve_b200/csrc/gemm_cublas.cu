@@ -67,3 +67,36 @@ SB_EXPORT int sb_linear(const void* a, const void* w, void* out, int M, int N, i
                         cudaStream_t stream) {
   return sb_linear_ld(a, K, w, out, N, M, N, K, in_dtype, out_dtype, stream);
 }
+
+// A batch of products with the batch index as a middle axis of both activations: out[m, b, :] = a[m, b, :] * w[b]^T for
+// every b. a is [M, B, K] with rows lda elements apart and batches a_batch apart; w is [B, N, K], whole; out is
+// [M, B, N] with rows ldc apart and batches c_batch apart (column slices of wider buffers on either side).
+SB_EXPORT int sb_linear_batched(const void* a, int lda, long long a_batch, const void* w, void* out, int ldc, long long c_batch, int M,
+                                int N, int K, int batch, int in_dtype, int out_dtype, cudaStream_t stream) {
+  if (M <= 0 || N <= 0 || batch <= 0) return 0;
+  if (K <= 0 || lda < K || ldc < N) return SB_ERR_SHAPE;
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return -103;
+  int rc = ensure_handle(dev);
+  if (rc) return rc;
+  cublasHandle_t h = g_handle[dev];
+  if (cublasSetStream(h, stream) != CUBLAS_STATUS_SUCCESS) return -104;
+  const float alpha = 1.f, beta = 0.f;
+  cudaDataType_t in_t, out_t;
+  cublasComputeType_t comp;
+  if (in_dtype == SB_DTYPE_F32) {
+    if (out_dtype != SB_DTYPE_F32) return SB_ERR_DTYPE;
+    in_t = CUDA_R_32F; out_t = CUDA_R_32F; comp = CUBLAS_COMPUTE_32F_PEDANTIC;
+  } else if (in_dtype == SB_DTYPE_BF16) {
+    in_t = CUDA_R_16BF; comp = CUBLAS_COMPUTE_32F;
+    if (out_dtype == SB_DTYPE_BF16) out_t = CUDA_R_16BF;
+    else if (out_dtype == SB_DTYPE_F32) out_t = CUDA_R_32F;
+    else return SB_ERR_DTYPE;
+  } else {
+    return SB_ERR_DTYPE;
+  }
+  cublasStatus_t st = cublasGemmStridedBatchedEx(h, CUBLAS_OP_T, CUBLAS_OP_N, N, M, K, &alpha, w, in_t, K, (long long)N * K, a, in_t, lda,
+                                                 a_batch, &beta, out, out_t, ldc, c_batch, batch, comp, CUBLAS_GEMM_DEFAULT);
+  if (st != CUBLAS_STATUS_SUCCESS) return -200 - (int)st;
+  return 0;
+}

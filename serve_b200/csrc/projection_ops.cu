@@ -1,0 +1,357 @@
+// What sits between a mixer's input projection and its attention, for mixers that do not rotate all of every head:
+//
+//   sb_add_layernorm          x += delta; out = (x - mean) / sqrt(var + eps) * weight   (float residual stream)
+//   sb_normed_qk_cache_write  queries and keys divided by the root mean square of the token's whole projection (all
+//                             heads at once) and multiplied by a weight, queries also by a temperature that grows
+//                             with the logarithm of the position; keys and values into their cache pages
+//   sb_latent_prepare         latent attention: the latent vector normalised, the shared key part and every head's
+//                             rotated query part turned by position; one cache row per token
+//   sb_gated_activation       act(gate, up) of a fused gate/up product: silu(g) * u, or the clamped form
+//                             g <- min(g, limit), u <- clamp(u, -limit, limit), g * sigmoid(alpha g) * (u + 1)
+//
+// All arithmetic is float: sums of squares, means, the logarithm, angles (float(position) * frequency, full-precision
+// sincosf) and the activation; T is the storage type of activations and cache pages. Reductions run in a fixed order
+// that depends on the block size only, never on the batch.
+#include "common.cuh"
+
+using namespace sb;
+
+namespace {
+
+template <typename T> __device__ __forceinline__ float4 load4f(const T* p);
+template <> __device__ __forceinline__ float4 load4f<float>(const float* p) { return *reinterpret_cast<const float4*>(p); }
+template <> __device__ __forceinline__ float4 load4f<__nv_bfloat16>(const __nv_bfloat16* p) {
+  const uint2 u = *reinterpret_cast<const uint2*>(p);
+  const __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162*>(&u.x), b = *reinterpret_cast<const __nv_bfloat162*>(&u.y);
+  return make_float4(__low2float(a), __high2float(a), __low2float(b), __high2float(b));
+}
+template <typename T> __device__ __forceinline__ void store4f(T* p, float4 v);
+template <> __device__ __forceinline__ void store4f<float>(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
+template <> __device__ __forceinline__ void store4f<__nv_bfloat16>(__nv_bfloat16* p, float4 v) {
+  __nv_bfloat162 a = __floats2bfloat162_rn(v.x, v.y), b = __floats2bfloat162_rn(v.z, v.w);
+  uint2 u;
+  u.x = *reinterpret_cast<uint32_t*>(&a);
+  u.y = *reinterpret_cast<uint32_t*>(&b);
+  *reinterpret_cast<uint2*>(p) = u;
+}
+
+// ------------------------------------------------------------------------------------------- add + layer norm
+// One block per row; the row (after the addition) is kept in shared memory between the three passes: mean, mean of
+// squared deviations, output. With rows != nullptr, row b of the output comes from x[rows[b]] and x is not written.
+// VEC: four elements at a time (dim a multiple of 4, aligned pointers).
+template <typename T, typename W, bool VEC>
+__global__ void add_layernorm_kernel(float* __restrict__ x, const T* __restrict__ delta, const int* __restrict__ rows,
+                                     const W* __restrict__ weight, T* __restrict__ out, int dim, float eps) {
+  __shared__ float red[32];
+  extern __shared__ __align__(16) float rowbuf[];
+  const int b = blockIdx.x;
+  const int src_row = rows ? rows[b] : b;
+  float* xr = x + (size_t)src_row * dim;
+  const T* dr = delta ? delta + (size_t)src_row * dim : nullptr;
+  const bool write_x = !rows && dr;
+  float s = 0.f;
+  if (VEC) {
+    for (int i = threadIdx.x * 4; i < dim; i += blockDim.x * 4) {
+      float4 v = *reinterpret_cast<const float4*>(xr + i);
+      if (dr) {
+        const float4 d = load4f<T>(dr + i);
+        v.x += d.x; v.y += d.y; v.z += d.z; v.w += d.w;
+      }
+      *reinterpret_cast<float4*>(rowbuf + i) = v;
+      if (write_x) *reinterpret_cast<float4*>(xr + i) = v;
+      s += (v.x + v.y) + (v.z + v.w);
+    }
+  } else {
+    for (int i = threadIdx.x; i < dim; i += blockDim.x) {
+      float v = xr[i];
+      if (dr) v += to_float(dr[i]);
+      rowbuf[i] = v;
+      if (write_x) xr[i] = v;
+      s += v;
+    }
+  }
+  const float mean = block_sum(s, red) / (float)dim;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < dim; i += blockDim.x) {      // (the barriers inside block_sum have published the row)
+    const float d = rowbuf[i] - mean;
+    ss += d * d;
+  }
+  const float inv = 1.0f / sqrtf(block_sum(ss, red) / (float)dim + eps);
+  T* orow = out + (size_t)b * dim;
+  if (VEC) {
+    for (int i = threadIdx.x * 4; i < dim; i += blockDim.x * 4) {
+      const float4 v = *reinterpret_cast<const float4*>(rowbuf + i);
+      const float4 w = load4f<W>(weight + i);
+      store4f<T>(orow + i, make_float4((v.x - mean) * inv * w.x, (v.y - mean) * inv * w.y, (v.z - mean) * inv * w.z, (v.w - mean) * inv * w.w));
+    }
+  } else {
+    for (int i = threadIdx.x; i < dim; i += blockDim.x) orow[i] = from_float<T>((rowbuf[i] - mean) * inv * to_float(weight[i]));
+  }
+}
+
+template <typename T, typename W>
+int launch_add_layernorm(float* x, const void* delta, const int* rows, const void* weight, void* out, int n_rows, int dim, float eps,
+                         cudaStream_t stream) {
+  const size_t smem = (size_t)dim * sizeof(float);
+  if (smem > 200 * 1024) return SB_ERR_LIMIT;
+  const bool vec = (dim % 4) == 0 && aligned16(x) && aligned16(out) && aligned16(weight) && (!delta || aligned16(delta));
+  const int threads = dim >= 4096 ? 512 : (dim >= 1024 ? 256 : 128);
+  auto k = vec ? add_layernorm_kernel<T, W, true> : add_layernorm_kernel<T, W, false>;
+  if (smem > 48 * 1024) cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  k<<<n_rows, threads, smem, stream>>>(x, (const T*)delta, rows, (const W*)weight, (T*)out, dim, eps);
+  SB_LAUNCH_CHECK();
+  return 0;
+}
+
+// --------------------------------------------------------------------- whole-projection norm, temperature, cache write
+// proj [T, (H + 2 G) * D] (row stride given): H query heads, G key heads, G value heads, each padded to D elements (the
+// padding holds zeros). One block per token.
+template <typename T>
+__global__ void __launch_bounds__(256) normed_qk_cache_write_kernel(
+    T* __restrict__ proj, int stride, const int* __restrict__ positions, const int* __restrict__ token_row, int H, int G, int D,
+    int dim, const float* __restrict__ q_weight, const float* __restrict__ k_weight, float eps, float temp_coef, int temp_every,
+    T* __restrict__ kc, T* __restrict__ vc, const int* __restrict__ block_table, int bt_width, int ps, int num_pages, int write_cache,
+    int* __restrict__ errors) {
+  __shared__ float red[32];
+  const int t = blockIdx.x;
+  T* row = proj + (size_t)t * stride;
+  const int nq = H * D, nk = G * D;
+  const int pos = positions[t];
+  float inv_q = 1.f, inv_k = 1.f;
+  if (q_weight != nullptr) {
+    float sq = 0.f, sk = 0.f;
+    for (int i = threadIdx.x; i < nq; i += blockDim.x) { const float v = to_float(row[i]); sq += v * v; }
+    for (int i = threadIdx.x; i < nk; i += blockDim.x) { const float v = to_float(row[nq + i]); sk += v * v; }
+    sq = block_sum(sq, red);
+    sk = block_sum(sk, red);
+    inv_q = 1.0f / sqrtf(sq / (float)(H * dim) + eps);
+    inv_k = 1.0f / sqrtf(sk / (float)(G * dim) + eps);
+  }
+  float temp = 1.f;
+  if (temp_coef != 0.f) temp = 1.0f + temp_coef * logf((float)((pos + 1) / temp_every + 1));
+  for (int i = threadIdx.x; i < nq; i += blockDim.x) {
+    float v = to_float(row[i]);
+    if (q_weight != nullptr) v = v * inv_q * q_weight[i];
+    row[i] = from_float<T>(v * temp);
+  }
+  if (!write_cache) return;
+  const int blk = pos / ps;
+  const int page = (pos >= 0 && blk < bt_width) ? block_table[(size_t)token_row[t] * bt_width + blk] : -1;
+  if (page < 0 || page >= num_pages) {
+    if (threadIdx.x == 0) atomicAdd(errors, 1);
+    return;
+  }
+  const int within = pos - blk * ps;
+  for (int i = threadIdx.x; i < nk; i += blockDim.x) {
+    const int g = i / D, d = i - g * D;
+    const size_t off = (((size_t)page * G + g) * ps + within) * D + d;
+    float kv = to_float(row[nq + i]);
+    if (k_weight != nullptr) kv = kv * inv_k * k_weight[i];
+    kc[off] = from_float<T>(kv);
+    vc[off] = row[nq + nk + i];
+  }
+}
+
+// ------------------------------------------------------------------------------------------------ latent attention
+// proj [T, stride]: columns [0, n_q) are H query heads of (dim + rd) each, [n_q, n_q + rank) the latent vector, then rd
+// of the shared key part. Writes, per token: the cache row [c * inv_rms * weight | rotated key part | zeros] of D
+// elements (one key/value head), and for every head columns [rank, D) of q_lat [T, H * D]: the rotated query part,
+// then zeros (columns [0, rank) are the product of the plain query part with the keys' read-out matrix, made elsewhere).
+// Rotation: pairs (2 i, 2 i + 1), i < rot_dims / 2, angle = float(position) * inv_freq[i]; the rest passes unchanged.
+template <typename T>
+__global__ void __launch_bounds__(128) latent_prepare_kernel(
+    const T* __restrict__ proj, int stride, int n_q, const int* __restrict__ positions, const int* __restrict__ token_row,
+    const float* __restrict__ c_weight, float eps, const float* __restrict__ inv_freq, int rot_dims, int H, int dim, int rd, int rank,
+    int D, T* __restrict__ q_lat, T* __restrict__ kc, const int* __restrict__ block_table, int bt_width, int ps, int num_pages,
+    int write_cache, int* __restrict__ errors) {
+  __shared__ float red[32];
+  extern __shared__ float cs[];            // [rot_dims / 2][2]: cosine and sine of the token's angles
+  const int t = blockIdx.x;
+  const T* row = proj + (size_t)t * stride;
+  const int pos = positions[t];
+  const int half = rot_dims / 2;
+  for (int i = threadIdx.x; i < half; i += blockDim.x) {
+    float s, c;
+    sincosf((float)pos * inv_freq[i], &s, &c);
+    cs[2 * i] = c;
+    cs[2 * i + 1] = s;
+  }
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < rank; i += blockDim.x) { const float v = to_float(row[n_q + i]); ss += v * v; }
+  ss = block_sum(ss, red);                 // (its barriers also publish cs)
+  const float inv = 1.0f / sqrtf(ss / (float)rank + eps);
+  // element j of a rotated part whose plain values start at src
+  auto rotated = [&](const T* src, int j) -> float {
+    if (j >= rot_dims) return to_float(src[j]);
+    const int i = j >> 1;
+    const float u = to_float(src[2 * i]), v = to_float(src[2 * i + 1]);
+    return (j & 1) ? v * cs[2 * i] + u * cs[2 * i + 1] : u * cs[2 * i] - v * cs[2 * i + 1];
+  };
+  const int tail = D - rank;               // columns of a head after the latent part
+  for (int w = threadIdx.x; w < H * tail; w += blockDim.x) {
+    const int h = w / tail, j = w - h * tail;
+    const float v = j < rd ? rotated(row + (size_t)h * (dim + rd) + dim, j) : 0.f;
+    q_lat[((size_t)t * H + h) * D + rank + j] = from_float<T>(v);
+  }
+  if (!write_cache) return;
+  const int blk = pos / ps;
+  const int page = (pos >= 0 && blk < bt_width) ? block_table[(size_t)token_row[t] * bt_width + blk] : -1;
+  if (page < 0 || page >= num_pages) {
+    if (threadIdx.x == 0) atomicAdd(errors, 1);
+    return;
+  }
+  T* dst = kc + ((size_t)page * ps + (pos - blk * ps)) * D;
+  for (int i = threadIdx.x; i < D; i += blockDim.x) {
+    float v = 0.f;
+    if (i < rank) v = to_float(row[n_q + i]) * inv * c_weight[i];
+    else if (i < rank + rd) v = rotated(row + n_q + rank, i - rank);
+    dst[i] = from_float<T>(v);
+  }
+}
+
+// ------------------------------------------------------------------------------------------------ gated activation
+// gate_up [T, 2 I] (gate columns, then up columns) -> out [T, I]. kind 0: silu(g) * u; 1: the clamped form.
+template <typename T>
+__global__ void gated_activation_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int inter, size_t total, int kind, float limit,
+                                        float alpha) {
+  for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
+    const size_t t = idx / inter;
+    const int i = (int)(idx - t * inter);
+    float g = to_float(gate_up[t * 2 * inter + i]);
+    float u = to_float(gate_up[t * 2 * inter + inter + i]);
+    float y;
+    if (kind == 1) {
+      g = fminf(g, limit);
+      u = fminf(fmaxf(u, -limit), limit);
+      y = g / (1.0f + expf(-alpha * g)) * (u + 1.0f);
+    } else {
+      y = g / (1.0f + expf(-g)) * u;
+    }
+    out[idx] = from_float<T>(y);
+  }
+}
+
+// bfloat16, 8 outputs a thread (16 bytes of gate, 16 of up)
+__global__ void gated_activation_bf16_vec_kernel(const __nv_bfloat16* __restrict__ gate_up, __nv_bfloat16* __restrict__ out, int inter8,
+                                                 size_t total8, int kind, float limit, float alpha) {
+  for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total8; idx += (size_t)gridDim.x * blockDim.x) {
+    const size_t t = idx / inter8;
+    const int i = (int)(idx - t * inter8);
+    const uint4 gv = *reinterpret_cast<const uint4*>(gate_up + (t * 2 * inter8 + i) * 8);
+    const uint4 uv = *reinterpret_cast<const uint4*>(gate_up + (t * 2 * inter8 + inter8 + i) * 8);
+    const __nv_bfloat162* g2 = reinterpret_cast<const __nv_bfloat162*>(&gv);
+    const __nv_bfloat162* u2 = reinterpret_cast<const __nv_bfloat162*>(&uv);
+    uint4 ov;
+    __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&ov);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      float2 g = __bfloat1622float2(g2[k]), u = __bfloat1622float2(u2[k]);
+      float y0, y1;
+      if (kind == 1) {
+        g.x = fminf(g.x, limit); g.y = fminf(g.y, limit);
+        u.x = fminf(fmaxf(u.x, -limit), limit); u.y = fminf(fmaxf(u.y, -limit), limit);
+        y0 = g.x / (1.0f + expf(-alpha * g.x)) * (u.x + 1.0f);
+        y1 = g.y / (1.0f + expf(-alpha * g.y)) * (u.y + 1.0f);
+      } else {
+        y0 = g.x / (1.0f + expf(-g.x)) * u.x;
+        y1 = g.y / (1.0f + expf(-g.y)) * u.y;
+      }
+      o2[k] = __floats2bfloat162_rn(y0, y1);
+    }
+    *reinterpret_cast<uint4*>(out + idx * 8) = ov;
+  }
+}
+
+}  // namespace
+
+SB_EXPORT int sb_add_layernorm(float* x, const void* delta, const int* rows, const void* weight, int weight_dtype, void* out, int n_rows,
+                               int dim, float eps, int dtype, cudaStream_t stream) {
+  if (n_rows <= 0) return 0;
+  if (dim <= 0) return SB_ERR_SHAPE;
+  if (dtype == SB_DTYPE_F32) {
+    if (weight_dtype != SB_DTYPE_F32) return SB_ERR_DTYPE;
+    return launch_add_layernorm<float, float>(x, delta, rows, weight, out, n_rows, dim, eps, stream);
+  }
+  if (dtype == SB_DTYPE_BF16) {
+    if (weight_dtype == SB_DTYPE_F32) return launch_add_layernorm<__nv_bfloat16, float>(x, delta, rows, weight, out, n_rows, dim, eps, stream);
+    if (weight_dtype == SB_DTYPE_BF16)
+      return launch_add_layernorm<__nv_bfloat16, __nv_bfloat16>(x, delta, rows, weight, out, n_rows, dim, eps, stream);
+  }
+  return SB_ERR_DTYPE;
+}
+
+// q_weight, k_weight: float [H * D], [G * D] laid out like the padded projection, or both null (no norm).
+SB_EXPORT int sb_normed_qk_cache_write(void* proj, int stride, const int* positions, const int* token_row, int H, int G, int D, int dim,
+                                       const float* q_weight, const float* k_weight, float eps, float temp_coef, int temp_every, void* kc,
+                                       void* vc, const int* block_table, int bt_width, int ps, int num_pages, int write_cache, int* errors,
+                                       int n_tokens, int dtype, cudaStream_t stream) {
+  if (n_tokens <= 0) return 0;
+  if (H <= 0 || G <= 0 || D <= 0 || dim <= 0 || dim > D || temp_every <= 0 || stride < (H + 2 * G) * D) return SB_ERR_SHAPE;
+  if ((q_weight == nullptr) != (k_weight == nullptr)) return SB_ERR_SHAPE;
+  if (write_cache && (ps <= 0 || bt_width <= 0 || !kc || !vc || !errors)) return SB_ERR_SHAPE;
+  if (dtype == SB_DTYPE_F32)
+    normed_qk_cache_write_kernel<float><<<n_tokens, 256, 0, stream>>>((float*)proj, stride, positions, token_row, H, G, D, dim, q_weight,
+                                                                       k_weight, eps, temp_coef, temp_every, (float*)kc, (float*)vc,
+                                                                       block_table, bt_width, ps, num_pages, write_cache, errors);
+  else if (dtype == SB_DTYPE_BF16)
+    normed_qk_cache_write_kernel<__nv_bfloat16><<<n_tokens, 256, 0, stream>>>(
+        (__nv_bfloat16*)proj, stride, positions, token_row, H, G, D, dim, q_weight, k_weight, eps, temp_coef, temp_every, (__nv_bfloat16*)kc,
+        (__nv_bfloat16*)vc, block_table, bt_width, ps, num_pages, write_cache, errors);
+  else
+    return SB_ERR_DTYPE;
+  SB_LAUNCH_CHECK();
+  return 0;
+}
+
+SB_EXPORT int sb_latent_prepare(const void* proj, int stride, int n_q, const int* positions, const int* token_row, const float* c_weight,
+                                float eps, const float* inv_freq, int rot_dims, int H, int dim, int rd, int rank, int D, void* q_lat,
+                                void* kc, const int* block_table, int bt_width, int ps, int num_pages, int write_cache, int* errors,
+                                int n_tokens, int dtype, cudaStream_t stream) {
+  if (n_tokens <= 0) return 0;
+  if (H <= 0 || dim <= 0 || rd <= 0 || rank <= 0 || rot_dims < 0 || (rot_dims & 1) || rot_dims > rd || D < rank + rd ||
+      n_q != H * (dim + rd) || stride < n_q + rank + rd)
+    return SB_ERR_SHAPE;
+  if (write_cache && (ps <= 0 || bt_width <= 0 || !kc || !errors)) return SB_ERR_SHAPE;
+  const size_t smem = (size_t)(rot_dims > 0 ? rot_dims : 2) * sizeof(float);
+  if (smem > 48 * 1024) return SB_ERR_LIMIT;
+  if (dtype == SB_DTYPE_F32)
+    latent_prepare_kernel<float><<<n_tokens, 128, smem, stream>>>((const float*)proj, stride, n_q, positions, token_row, c_weight, eps,
+                                                                   inv_freq, rot_dims, H, dim, rd, rank, D, (float*)q_lat, (float*)kc,
+                                                                   block_table, bt_width, ps, num_pages, write_cache, errors);
+  else if (dtype == SB_DTYPE_BF16)
+    latent_prepare_kernel<__nv_bfloat16><<<n_tokens, 128, smem, stream>>>(
+        (const __nv_bfloat16*)proj, stride, n_q, positions, token_row, c_weight, eps, inv_freq, rot_dims, H, dim, rd, rank, D,
+        (__nv_bfloat16*)q_lat, (__nv_bfloat16*)kc, block_table, bt_width, ps, num_pages, write_cache, errors);
+  else
+    return SB_ERR_DTYPE;
+  SB_LAUNCH_CHECK();
+  return 0;
+}
+
+SB_EXPORT int sb_gated_activation(const void* gate_up, void* out, int n_tokens, int inter, int kind, float limit, float alpha, int dtype,
+                                  cudaStream_t stream) {
+  if (n_tokens <= 0) return 0;
+  if (inter <= 0 || kind < 0 || kind > 1) return SB_ERR_SHAPE;
+  const size_t total = (size_t)n_tokens * inter;
+  const int threads = 256;
+  if (dtype == SB_DTYPE_BF16 && (inter % 8) == 0 && aligned16(gate_up) && aligned16(out)) {
+    const size_t total8 = total / 8;
+    const size_t want = (total8 + threads - 1) / threads;
+    const int blocks = (int)(want < (size_t)sm_count() * 16 ? want : (size_t)sm_count() * 16);
+    gated_activation_bf16_vec_kernel<<<blocks, threads, 0, stream>>>((const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, inter / 8, total8,
+                                                                     kind, limit, alpha);
+    SB_LAUNCH_CHECK();
+    return 0;
+  }
+  const size_t want = (total + threads - 1) / threads;
+  const int blocks = (int)(want < (size_t)sm_count() * 16 ? want : (size_t)sm_count() * 16);
+  if (dtype == SB_DTYPE_F32)
+    gated_activation_kernel<float><<<blocks, threads, 0, stream>>>((const float*)gate_up, (float*)out, inter, total, kind, limit, alpha);
+  else if (dtype == SB_DTYPE_BF16)
+    gated_activation_kernel<__nv_bfloat16><<<blocks, threads, 0, stream>>>((const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, inter, total,
+                                                                           kind, limit, alpha);
+  else
+    return SB_ERR_DTYPE;
+  SB_LAUNCH_CHECK();
+  return 0;
+}

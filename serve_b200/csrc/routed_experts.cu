@@ -10,6 +10,8 @@
 //      token. The weight multiplies the expert's input; a product is linear, so it is applied to the float sums.
 //   4. sb_moe_down: out[pair] = act[row] W_down^T, written at the pair's own place; with top == 1 that is the result,
 //      otherwise sb_moe_combine adds a token's `top` rows in order.
+// Experts without a gate (sb_moe_up: act[row] = f(x W_up^T), f = relu squared) and a choice that is read from a table
+// over token ids instead of router logits (sb_moe_route_table) go through the same grouping and the same down product.
 // Products accumulate in float over k in ascending order, whatever else is in the step.
 #include "common.cuh"
 
@@ -125,13 +127,34 @@ __global__ void __launch_bounds__(1024) moe_sort_kernel(const int* __restrict__ 
   }
 }
 
+// The experts of a token from a table over token ids: idx[t, j] = table[token[t], j], every weight 1 / top. A token id
+// below zero, -(s + 1), stands for the token last sampled for state slot s (as in the embedding kernel).
+__global__ void __launch_bounds__(256) moe_route_table_kernel(const int* __restrict__ tokens, const int* __restrict__ last_token,
+                                                              int n_slots, const int* __restrict__ table, int vocab, int E, int top,
+                                                              int n_tokens, int* __restrict__ idx, float* __restrict__ wts,
+                                                              int* __restrict__ errors) {
+  const int w = blockIdx.x * blockDim.x + threadIdx.x;
+  if (w >= n_tokens * top) return;
+  const int t = w / top, j = w - t * top;
+  int tok = tokens[t];
+  if (tok < 0 && last_token != nullptr && -tok - 1 < n_slots) tok = last_token[-tok - 1];
+  int e = (tok >= 0 && tok < vocab) ? table[(size_t)tok * top + j] : -1;
+  if (e < 0 || e >= E) {
+    atomicAdd(errors, 1);        // a token outside the table or an entry outside the experts: counted, expert 0 stands in
+    e = 0;
+  }
+  idx[w] = e;
+  wts[w] = 1.0f / (float)top;
+}
+
 constexpr int TK = 32;
 constexpr int GU_COLS = 32;       // gate columns of a tile (and as many up columns)
 constexpr int DN_COLS = 64;
 constexpr int MOE_THREADS = 256;
 
 // grid (column tiles of ff, row tiles). x [T, K] with row stride; w_gu [E, 2 ff, K] (gate rows, then up rows).
-// act kinds: 0 = silu(g) * u; 1 = the clamped form: g <- min(g, limit), u <- clamp(u, -limit, limit), g * sigmoid(alpha g) * (u + 1).
+// act kinds: 0 = silu(g) * u; 1 = the clamped form: g <- min(g, limit), u <- clamp(u, -limit, limit), g * sigmoid(alpha g) * (u + 1);
+// 2 = no gate: w_gu is [E, ff, K] and the output is relu(x W^T)^2.
 template <typename T>
 __global__ void __launch_bounds__(MOE_THREADS) moe_gate_up_kernel(const T* __restrict__ x, int x_stride, const T* __restrict__ w_gu,
                                                                   const int* __restrict__ order, const int* __restrict__ offsets,
@@ -154,7 +177,8 @@ __global__ void __launch_bounds__(MOE_THREADS) moe_gate_up_kernel(const T* __res
     rw[tid] = pair >= 0 ? wts[pair] : 0.f;
   }
   __syncthreads();
-  const T* wg = w_gu + (size_t)e * 2 * ff * K;
+  const bool gated = act_kind != 2;
+  const T* wg = w_gu + (size_t)e * (gated ? 2 : 1) * ff * K;
   const T* wu = wg + (size_t)ff * K;
   const int ty = tid >> 4, tx = tid & 15;               // rows 2 ty, 2 ty + 1; columns 2 tx, 2 tx + 1
   float ag[2][2] = {{0.f, 0.f}, {0.f, 0.f}}, au[2][2] = {{0.f, 0.f}, {0.f, 0.f}};
@@ -168,7 +192,7 @@ __global__ void __launch_bounds__(MOE_THREADS) moe_gate_up_kernel(const T* __res
       const int nn = w / TK, kk = w - nn * TK;
       const bool ok = n0 + nn < ff && k0 + kk < K;
       Bg[kk][nn] = ok ? to_float(wg[(size_t)(n0 + nn) * K + k0 + kk]) : 0.f;
-      Bu[kk][nn] = ok ? to_float(wu[(size_t)(n0 + nn) * K + k0 + kk]) : 0.f;
+      Bu[kk][nn] = (ok && gated) ? to_float(wu[(size_t)(n0 + nn) * K + k0 + kk]) : 0.f;
     }
     __syncthreads();
 #pragma unroll 8
@@ -190,7 +214,10 @@ __global__ void __launch_bounds__(MOE_THREADS) moe_gate_up_kernel(const T* __res
       const int nn = n0 + 2 * tx + jx;
       if (nn >= ff) continue;
       float g = ag[i][jx] * sc, u = au[i][jx] * sc, yv;
-      if (act_kind == 1) {
+      if (act_kind == 2) {
+        g = fmaxf(g, 0.f);
+        yv = g * g;
+      } else if (act_kind == 1) {
         g = fminf(g, limit);
         u = fminf(fmaxf(u, -limit), limit);
         yv = g * sigmoid_f(alpha * g) * (u + 1.f);
@@ -404,6 +431,47 @@ __global__ void __launch_bounds__(MB_THREADS) moe_gate_up_mma_kernel(
     }
 }
 
+// The product without a gate: grid (ceil(ff / 64), row tiles of MB_M rows); w_up [E, ff, K]; act = relu(x W^T)^2.
+__global__ void __launch_bounds__(MB_THREADS) moe_up_mma_kernel(
+    const __nv_bfloat16* __restrict__ x, int x_stride, const __nv_bfloat16* __restrict__ w_up, const int* __restrict__ order,
+    const int* __restrict__ offsets, const int* __restrict__ tiles, const int* __restrict__ n_tiles, int top, int K, int ff,
+    __nv_bfloat16* __restrict__ act) {
+  if ((int)blockIdx.y >= n_tiles[0]) return;
+  extern __shared__ __align__(16) unsigned char raw[];
+  __nv_bfloat16* smem = (__nv_bfloat16*)raw;
+  __shared__ int tok[MB_M];
+  const int e = tiles[2 * blockIdx.y], row0 = tiles[2 * blockIdx.y + 1];
+  const int rows = min(MB_M, offsets[e + 1] - row0);
+  const int n0 = blockIdx.x * MB_N;
+  const int tid = threadIdx.x;
+  if (tid < MB_M) {
+    const int pair = tid < rows ? order[row0 + tid] : -1;
+    tok[tid] = pair >= 0 ? pair / top : -1;
+  }
+  __syncthreads();
+  const __nv_bfloat16* w = w_up + (size_t)e * ff * K;
+  float acc[2][4][4] = {};
+  mma_tile_loop([&](int m) -> const __nv_bfloat16* { return tok[m] >= 0 ? x + (size_t)tok[m] * x_stride : nullptr; },
+                [&](int n) -> const __nv_bfloat16* { return n0 + n < ff ? w + (size_t)(n0 + n) * K : nullptr; }, w, K, smem, acc);
+  const int lane = tid & 31, warp = tid >> 5, wm = warp >> 1, wn = warp & 1;
+#pragma unroll
+  for (int i = 0; i < 2; ++i)
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+      const int m = wm * 32 + i * 16 + (lane >> 2) + half * 8;
+      if (m >= rows) continue;
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+#pragma unroll
+        for (int c = 0; c < 2; ++c) {
+          const int col = n0 + wn * 32 + j * 8 + (lane & 3) * 2 + c;
+          if (col >= ff) continue;
+          const float g = fmaxf(acc[i][j][half * 2 + c], 0.f);
+          act[(size_t)(row0 + m) * ff + col] = __float2bfloat16_rn(g * g);
+        }
+    }
+}
+
 // grid (ceil(N / 64), row tiles).
 template <typename O>
 __global__ void __launch_bounds__(MB_THREADS) moe_down_mma_kernel(const __nv_bfloat16* __restrict__ act, const __nv_bfloat16* __restrict__ w_down,
@@ -510,6 +578,49 @@ SB_EXPORT int sb_moe_gate_up(const void* x, int x_stride, const void* w_gu, cons
     moe_gate_up_kernel<__nv_bfloat16><<<grid, MOE_THREADS, 0, stream>>>((const __nv_bfloat16*)x, x_stride, (const __nv_bfloat16*)w_gu,
                                                                          order, offsets, tiles, n_tiles, wts, top, K, ff, scale_input,
                                                                          act_kind, limit, alpha, (__nv_bfloat16*)act);
+  else
+    return SB_ERR_DTYPE;
+  SB_LAUNCH_CHECK();
+  return 0;
+}
+
+// tokens int32 [T] -> idx int32 [T, top], wts float [T, top] from table int32 [vocab, top]; ``errors``: a counter that
+// receives tokens outside the table and entries outside 0 .. E-1.
+SB_EXPORT int sb_moe_route_table(const int* tokens, const int* last_token, int n_slots, const int* table, int vocab, int E, int top,
+                                 int n_tokens, int* idx, float* wts, int* errors, cudaStream_t stream) {
+  if (n_tokens <= 0) return 0;
+  if (E <= 0 || top <= 0 || top > E || vocab <= 0 || !errors) return SB_ERR_SHAPE;
+  const int total = n_tokens * top;
+  moe_route_table_kernel<<<(total + 255) / 256, 256, 0, stream>>>(tokens, last_token, n_slots, table, vocab, E, top, n_tokens, idx, wts,
+                                                                  errors);
+  SB_LAUNCH_CHECK();
+  return 0;
+}
+
+// The experts' first product without a gate: act [n_pairs rows in grouped order, ff] = relu(x W_up^T)^2, w_up [E, ff, K].
+SB_EXPORT int sb_moe_up(const void* x, int x_stride, const void* w_up, const int* order, const int* offsets, const int* tiles,
+                        const int* n_tiles, const float* wts, int top, int n_pairs, int E, int K, int ff, void* act, int dtype,
+                        cudaStream_t stream) {
+  if (n_pairs <= 0) return 0;
+  const int tile_rows = sb_moe_tile_rows(dtype, K, ff, x_stride);
+  const int max_tiles = n_pairs / tile_rows + (E < n_pairs ? E : n_pairs);
+  if (max_tiles > 65535) return SB_ERR_LIMIT;
+  if (tile_rows == MB_M) {
+    if (!aligned16(x) || !aligned16(w_up)) return SB_ERR_ALIGN;
+    cudaFuncSetAttribute(moe_up_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)MB_SMEM);
+    moe_up_mma_kernel<<<dim3((ff + MB_N - 1) / MB_N, max_tiles), MB_THREADS, MB_SMEM, stream>>>(
+        (const __nv_bfloat16*)x, x_stride, (const __nv_bfloat16*)w_up, order, offsets, tiles, n_tiles, top, K, ff, (__nv_bfloat16*)act);
+    SB_LAUNCH_CHECK();
+    return 0;
+  }
+  dim3 grid((ff + GU_COLS - 1) / GU_COLS, max_tiles);
+  if (dtype == SB_DTYPE_F32)
+    moe_gate_up_kernel<float><<<grid, MOE_THREADS, 0, stream>>>((const float*)x, x_stride, (const float*)w_up, order, offsets, tiles,
+                                                                 n_tiles, wts, top, K, ff, 0, 2, 0.f, 0.f, (float*)act);
+  else if (dtype == SB_DTYPE_BF16)
+    moe_gate_up_kernel<__nv_bfloat16><<<grid, MOE_THREADS, 0, stream>>>((const __nv_bfloat16*)x, x_stride, (const __nv_bfloat16*)w_up,
+                                                                         order, offsets, tiles, n_tiles, wts, top, K, ff, 0, 2, 0.f, 0.f,
+                                                                         (__nv_bfloat16*)act);
   else
     return SB_ERR_DTYPE;
   SB_LAUNCH_CHECK();

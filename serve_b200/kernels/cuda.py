@@ -72,8 +72,18 @@ def core_jobs():
 
 
 def sequence_job():
-    """Kernels of the mixers with recurrent state and of routed experts (built when a model first asks for them)."""
-    return {"name": "sb_seq", "sources": ["sequence_ops.cu", "routed_experts.cu"]}
+    """Kernels of the mixers with recurrent state (built when a model first asks for them)."""
+    return {"name": "sb_seq", "sources": ["sequence_ops.cu"]}
+
+
+def experts_job():
+    """Kernels of feed-forwards made of experts (built when a model first asks for them)."""
+    return {"name": "sb_moe", "sources": ["routed_experts.cu"]}
+
+
+def projection_job():
+    """Layer norm, whole-projection query/key norm with temperature, latent-attention preparation, gated activations."""
+    return {"name": "sb_prep", "sources": ["projection_ops.cu"]}
 
 
 def attention_job(head_dim: int):
@@ -113,7 +123,7 @@ class LayerRunPlan:
 
 def all_jobs():
     """Every library the engine can ask for (the build check compiles them all)."""
-    return (core_jobs() + [sequence_job()] + [attention_job(d) for d in SUPPORTED_HEAD_DIMS]
+    return (core_jobs() + [sequence_job(), experts_job(), projection_job()] + [attention_job(d) for d in SUPPORTED_HEAD_DIMS]
             + [layer_run_job(d) for d in LAYER_RUN_HEAD_DIMS])
 
 
@@ -158,6 +168,8 @@ class CudaKernels:
         # off unless asked for (tests, and SERVE_B200_LAYER_RUNS=1 for measurements).
         self.use_layer_runs = os.environ.get("SERVE_B200_LAYER_RUNS", "0") == "1"
         self._seq = None                     # the library of sequence_job(), loaded at first use
+        self._moe = None                     # the library of experts_job(), loaded at first use
+        self._prep = None                    # the library of projection_job(), loaded at first use
         self._stack: Dict[int, ctypes.CDLL] = {}
         self._stack_sync = None              # two counters of the layer-run kernel's grid barrier (zero between launches)
         self._stack_partials = None
@@ -195,6 +207,24 @@ class CudaKernels:
             lib = self._attn[head_dim] = ctypes.CDLL(path)
             lib.sb_attention_mma_scratch_bytes.restype = ctypes.c_longlong
         return lib
+
+    def prepare(self, head_dims=(), libraries=()) -> None:
+        """Build side by side, and load, what a model is going to call: attention libraries for ``head_dims`` and the
+        optional libraries named ("seq", "moe", "prep"). Without this each is built when first called."""
+        named = {"seq": sequence_job, "moe": experts_job, "prep": projection_job}
+        jobs = [attention_job(d) for d in sorted(set(head_dims)) if d not in self._attn]
+        for d in head_dims:
+            self.check_attention_shape(1, 1, d)
+        jobs += [named[n]() for n in sorted(set(libraries)) if getattr(self, "_" + n) is None]
+        if not jobs:
+            return
+        for j in jobs:
+            j["verbose"] = self._verbose
+        self.paths.update(build.build_many(jobs))
+        for d in head_dims:
+            self._attention_lib(d)
+        for n in libraries:
+            getattr(self, f"_{n}_lib")()
 
     def errors_tensor(self) -> torch.Tensor:
         if self._errors is None:
@@ -236,12 +266,12 @@ class CudaKernels:
         self.launches += 1
         _check(self._core.sb_fetch_ints(_p(host_pinned), _p(dev), n, self._s()), "fetch of the step's inputs")
 
-    def embedding(self, tokens, table, out, last_token=None) -> None:
-        """out[t] = table[tokens[t]]; an id -(s+1) is replaced by last_token[s] (the token last sampled for slot s)."""
+    def embedding(self, tokens, table, out, last_token=None, scale: float = 1.0) -> None:
+        """out[t] = table[tokens[t]] * scale; an id -(s+1) is replaced by last_token[s] (the token last sampled for slot s)."""
         self.launches += 1
         _check(self._core.sb_embedding(_p(tokens), _p(table), _p(out), tokens.shape[0], table.shape[1], table.shape[0],
                                        _DT[table.dtype], _p(last_token), last_token.shape[0] if last_token is not None else 0,
-                                       self._s()), "embedding")
+                                       ctypes.c_float(scale), self._s()), "embedding")
 
     def add_rmsnorm(self, x, delta, weight, eps, out) -> None:
         self.launches += 1
@@ -252,6 +282,67 @@ class CudaKernels:
         self.launches += 1
         _check(self._core.sb_add_rmsnorm(_p(x), _p(delta), _p(rows), _p(weight), _DT[weight.dtype], _p(out), rows.shape[0],
                                          x.shape[1], ctypes.c_float(eps), _DT[out.dtype], self._s()), "add_rmsnorm_rows")
+
+    def add_layernorm(self, x, delta, weight, eps, out) -> None:
+        """x += delta; out = (x - mean) / sqrt(var + eps) * weight, row by row (x float, updated in place)."""
+        self.launches += 1
+        _check(self._prep_lib().sb_add_layernorm(_p(x), _p(delta), _p(None), _p(weight), _DT[weight.dtype], _p(out), x.shape[0],
+                                                 x.shape[1], ctypes.c_float(eps), _DT[out.dtype], self._s()), "add_layernorm")
+
+    def add_layernorm_rows(self, x, delta, rows, weight, eps, out) -> None:
+        self.launches += 1
+        _check(self._prep_lib().sb_add_layernorm(_p(x), _p(delta), _p(rows), _p(weight), _DT[weight.dtype], _p(out), rows.shape[0],
+                                                 x.shape[1], ctypes.c_float(eps), _DT[out.dtype], self._s()), "add_layernorm_rows")
+
+    def linear_batched(self, a, w, out) -> None:
+        """out[:, b] = a[:, b] @ w[b]^T for every b: a [M, B, K] and out [M, B, N] may be views of wider buffers (unit stride
+        along the last axis), w [B, N, K] is whole. One batched library product."""
+        m, b, k = a.shape
+        n = w.shape[1]
+        if (w.shape[0] != b or w.shape[2] != k or tuple(out.shape) != (m, b, n) or a.dtype != w.dtype or a.stride(2) != 1
+                or out.stride(2) != 1 or not w.is_contiguous()):
+            raise KernelError(f"linear_batched: a {tuple(a.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)} do not fit")
+        self.library_calls += 1
+        _check(self._gemm.sb_linear_batched(_p(a), a.stride(0), ctypes.c_longlong(a.stride(1)), _p(w), _p(out), out.stride(0),
+                                            ctypes.c_longlong(out.stride(1)), m, n, k, b, _DT[a.dtype], _DT[out.dtype], self._s()),
+               "batched linear")
+
+    def gate_up_activation(self, h, w_gate_up, out, activation: str, limit: float = 0.0, alpha: float = 1.0) -> None:
+        """out[T, I] = act(h @ w_gate^T, h @ w_up^T), w_gate_up = [w_gate; w_up]: "swiglu" or "clamped_swish" (g <- min(g, limit),
+        u <- clamp(u, -limit, limit), g * sigmoid(alpha g) * (u + 1)); the product is the library's or the few-rows kernel's."""
+        if activation == "swiglu":
+            return self.gate_up_swiglu(h, w_gate_up, out)
+        t, inter = h.shape[0], out.shape[1]
+        if w_gate_up.shape[0] != 2 * inter or w_gate_up.shape[1] != h.shape[1] or out.shape[0] != t:
+            raise KernelError("gate_up_activation: shapes do not fit")
+        gate_up = torch.empty((t, 2 * inter), dtype=h.dtype, device=h.device)
+        self.linear(h, w_gate_up, gate_up)
+        self.launches += 1
+        _check(self._prep_lib().sb_gated_activation(_p(gate_up), _p(out), t, inter, {"clamped_swish": 1}[activation], ctypes.c_float(limit),
+                                                    ctypes.c_float(alpha), _DT[out.dtype], self._s()), "gated activation")
+
+    def normed_qk_cache_write(self, proj, positions, token_row, heads, kv_heads, head_dim, dim, q_weight, k_weight, eps, temp_coef,
+                              temp_every, k_cache, v_cache, block_table, page_size, write_cache) -> None:
+        """proj [T, (H + 2 G) * D] (heads padded to D with zeros): queries and keys divided by the root mean square over the
+        token's whole projection (H * dim, G * dim true elements) and multiplied by float weights [H * D], [G * D] (None: no
+        norm); queries then times 1 + temp_coef * ln(floor((p + 1) / temp_every) + 1), in place; keys and values to the pages."""
+        self.launches += 1
+        _check(self._prep_lib().sb_normed_qk_cache_write(
+            _p(proj), proj.stride(0), _p(positions), _p(token_row), heads, kv_heads, head_dim, dim, _p(q_weight), _p(k_weight),
+            ctypes.c_float(eps), ctypes.c_float(temp_coef), int(temp_every), _p(k_cache), _p(v_cache), _p(block_table), block_table.shape[1],
+            page_size, k_cache.shape[0], 1 if write_cache else 0, _p(self.errors_tensor()), proj.shape[0], _DT[proj.dtype], self._s()),
+            "query/key norm and cache write")
+
+    def latent_prepare(self, proj, n_q, positions, token_row, c_weight, eps, inv_freq, rot_dims, heads, dim, rot_dim, rank, head_dim,
+                       q_lat, k_cache, block_table, page_size, write_cache) -> None:
+        """Latent attention between its input product and its attention: proj [T, >= n_q + rank + rot_dim] holds the heads'
+        queries ([dim | rot_dim] each), the latent vector and the shared key part. Writes the cache row [normed latent | rotated
+        key part | zeros] and columns [rank, head_dim) of every head of q_lat (rotated query part, zeros)."""
+        self.launches += 1
+        _check(self._prep_lib().sb_latent_prepare(
+            _p(proj), proj.stride(0), n_q, _p(positions), _p(token_row), _p(c_weight), ctypes.c_float(eps), _p(inv_freq), rot_dims, heads,
+            dim, rot_dim, rank, head_dim, _p(q_lat), _p(k_cache), _p(block_table), block_table.shape[1], page_size, k_cache.shape[0],
+            1 if write_cache else 0, _p(self.errors_tensor()), proj.shape[0], _DT[proj.dtype], self._s()), "latent attention preparation")
 
     def linear(self, a, w, out) -> None:
         """out[M,N] = a[M,K] @ w[N,K]^T (library matrix product)."""
@@ -377,21 +468,24 @@ class CudaKernels:
                               k_cache, v_cache, block_table, page_size, write_cache)
 
     def attention(self, qkv, k_cache, v_cache, block_table, cu_q, kv_len, token_row, positions, heads, kv_heads, head_dim,
-                  page_size, scale, window, out, shape, slopes=None, chunk: int = 0) -> None:
+                  page_size, scale, window, out, shape, slopes=None, chunk: int = 0, softcap: float = 0.0, sinks=None) -> None:
         """``slopes`` (float [heads]): slope_h * distance is taken off every score; ``chunk`` > 0: a query sees only the keys of
-        its own block of ``chunk`` positions. In bfloat16 both run on the mma.sync kernels (the tensor-memory kernel takes
-        neither), in float32 on the plain-arithmetic kernel."""
+        its own block of ``chunk`` positions; ``softcap`` c > 0: a scaled score s becomes c * tanh(s / c); ``sinks`` (float
+        [heads]): exp(sink_h) joins the softmax's denominator. In bfloat16 all run on the mma.sync kernels (the tensor-memory
+        kernel takes none of them), in float32 on the plain-arithmetic kernel."""
         lib = self._attention_lib(head_dim)
-        if (slopes is not None or chunk) and qkv.dtype == torch.bfloat16 and not self.force_simt_attention:
+        softcap = float(softcap or 0.0)
+        opts = slopes is not None or chunk or softcap > 0.0 or sinks is not None
+        if opts and qkv.dtype == torch.bfloat16 and not self.force_simt_attention:
             return self._attention_mma(lib, qkv, k_cache, v_cache, block_table, cu_q, kv_len, heads, kv_heads, head_dim,
-                                       page_size, scale, window, out, shape, slopes=slopes, chunk=int(chunk))
-        if slopes is not None or chunk:
+                                       page_size, scale, window, out, shape, slopes=slopes, chunk=int(chunk), softcap=softcap, sinks=sinks)
+        if opts:
             group = heads // kv_heads
             self.launches += (1 if group <= 16 else 0) + (1 if group > 16 or shape.max_q * group > 16 else 0)
-            _check(lib.sb_attention_simt_biased(
+            _check(lib.sb_attention_simt_opts(
                 _p(qkv), qkv.stride(0), _p(k_cache), _p(v_cache), _p(block_table), block_table.shape[1], _p(cu_q), _p(kv_len),
                 heads, kv_heads, page_size, k_cache.shape[0], ctypes.c_float(scale), window, _p(out), shape.rows, shape.max_q,
-                _DT[qkv.dtype], _p(slopes), int(chunk), self._s()), "attention with distance bias")
+                _DT[qkv.dtype], _p(slopes), int(chunk), ctypes.c_float(softcap), _p(sinks), self._s()), "attention with score options")
             return
         if qkv.dtype == torch.bfloat16 and not self.force_simt_attention:
             return self._attention_mma(lib, qkv, k_cache, v_cache, block_table, cu_q, kv_len, heads, kv_heads, head_dim,
@@ -416,7 +510,7 @@ class CudaKernels:
         return max(1, min(want, -(-max_kv // 256), self.MAX_SPLITS))
 
     def _attention_mma(self, lib, qkv, k_cache, v_cache, block_table, cu_q, kv_len, heads, kv_heads, head_dim, page_size,
-                       scale, window, out, shape, slopes=None, chunk: int = 0) -> None:
+                       scale, window, out, shape, slopes=None, chunk: int = 0, softcap: float = 0.0, sinks=None) -> None:
         group = heads // kv_heads
         min_q = getattr(shape, "min_q", 1)
         which = 0
@@ -443,7 +537,7 @@ class CudaKernels:
             if num_splits > 1:
                 scratch = self._scratch_buffer(lib, shape.rows, kv_heads, num_splits)
                 tickets = self._ticket_buffer(shape.rows * kv_heads)
-        by_distance = slopes is not None or chunk > 0
+        by_distance = slopes is not None or chunk > 0 or softcap > 0.0 or sinks is not None
         if (which & 1) and not by_distance and self.use_tcgen05_attention and self._tc_attention_takes(lib, heads, kv_heads, head_dim, page_size, window, qkv.shape[1]):
             # prompt portions on the tensor-memory path; what is left (decoding rows) goes to the deep shape below
             self.launches += 1
@@ -456,11 +550,11 @@ class CudaKernels:
             if not which:
                 return
         self.launches += (which & 1) + ((which >> 1) & 1) + ((which >> 2) & 1)
-        _check(lib.sb_attention_mma_biased(
+        _check(lib.sb_attention_mma_opts(
             _p(qkv), qkv.stride(0), _p(k_cache), _p(v_cache), _p(block_table), block_table.shape[1], _p(cu_q), _p(kv_len),
             heads, kv_heads, page_size, k_cache.shape[0], ctypes.c_float(scale), window, _p(out), shape.rows, shape.max_q,
-            which, int(shape.max_kv), num_splits, _p(scratch), _p(tickets), _p(wide_rows), n_wide, _p(slopes), chunk, self._s()),
-            "attention")
+            which, int(shape.max_kv), num_splits, _p(scratch), _p(tickets), _p(wide_rows), n_wide, _p(slopes), chunk,
+            ctypes.c_float(softcap), _p(sinks), self._s()), "attention")
 
     def _tc_attention_takes(self, lib, heads, kv_heads, head_dim, page_size, window, stride) -> bool:
         key = (heads, kv_heads, head_dim, page_size, window, stride)
@@ -621,6 +715,24 @@ class CudaKernels:
             self._seq = ctypes.CDLL(path)
         return self._seq
 
+    def _moe_lib(self):
+        if self._moe is None:
+            job = experts_job()
+            job["verbose"] = self._verbose
+            path = build.build_library(**job)
+            self.paths[job["name"]] = path
+            self._moe = ctypes.CDLL(path)
+        return self._moe
+
+    def _prep_lib(self):
+        if self._prep is None:
+            job = projection_job()
+            job["verbose"] = self._verbose
+            path = build.build_library(**job)
+            self.paths[job["name"]] = path
+            self._prep = ctypes.CDLL(path)
+        return self._prep
+
     def causal_conv(self, x, weight, bias, state, ctx, out, activation: str = "none", residual: bool = False) -> None:
         """out[t] = act(bias + sum_j weight[:, j] * x[t - taps + 1 + j] (+ x[t])) per channel, over each request's own tokens;
         the taps - 1 inputs before a portion come from ``state`` [slots, taps - 1, C] (float), which then takes the portion's
@@ -681,7 +793,7 @@ class CudaKernels:
                        scale_input: bool = True, activation: str = "clamped_swish", limit: float = 0.0, alpha: float = 1.702) -> None:
         """out[t] = sum over the ``top`` best experts e of expert_e(w_e * h[t]) (or w_e * expert_e(h[t])): logits float [T, E],
         w_gate_up [E, 2 ff, K], w_down [E, N, ff]."""
-        lib = self._seq_lib()
+        lib = self._moe_lib()
         t, e = logits.shape
         ff, n, k = w_down.shape[2], w_down.shape[1], h.shape[1]
         pairs = t * top
@@ -706,6 +818,40 @@ class CudaKernels:
         parts = out if top == 1 else torch.empty((pairs, n), dtype=torch.float32, device=dev)
         _check(lib.sb_moe_down(_p(act), _p(w_down), _p(order), _p(offsets), _p(tiles), _p(n_tiles), _p(wts), pairs, e, ff, n,
                                0 if scale_input else 1, _p(parts), _DT[h.dtype], _DT[parts.dtype], tile_rows, s), "experts, down")
+        if top > 1:
+            self.launches += 1
+            _check(lib.sb_moe_combine(_p(parts), top, t, n, _p(out), _DT[out.dtype], s), "sum over a token's experts")
+
+    def table_experts(self, h, tokens, last_token, table, w_up, w_down, top: int, out, activation: str = "relu_squared") -> None:
+        """out[t] = (1 / top) * sum over the experts e = table[token[t], :] of w_down[e] act(w_up[e] h[t]), act = relu squared:
+        table int32 [vocab, top], w_up [E, ff, K], w_down [E, N, ff]. A token id -(s+1) stands for last_token[s]."""
+        if activation != "relu_squared":
+            raise KernelError(f"table_experts: activation {activation!r} is not known")
+        lib = self._moe_lib()
+        t = h.shape[0]
+        e, ff, k = w_up.shape
+        n = w_down.shape[1]
+        pairs = t * top
+        dev = h.device
+        tile_rows = lib.sb_moe_tile_rows(_DT[h.dtype], k, ff, h.stride(0))
+        max_tiles = pairs // tile_rows + min(e, pairs)
+        ints = torch.empty(2 * pairs + e + 1 + 2 * max_tiles + 1, dtype=torch.int32, device=dev)
+        idx, order = ints[:pairs], ints[pairs: 2 * pairs]
+        offsets = ints[2 * pairs: 2 * pairs + e + 1]
+        tiles = ints[2 * pairs + e + 1: 2 * pairs + e + 1 + 2 * max_tiles]
+        n_tiles = ints[-1:]
+        wts = torch.empty(pairs, dtype=torch.float32, device=dev)
+        s = self._s()
+        self.launches += 4
+        _check(lib.sb_moe_route_table(_p(tokens), _p(last_token), last_token.shape[0] if last_token is not None else 0, _p(table),
+                                      table.shape[0], e, top, t, _p(idx), _p(wts), _p(self.errors_tensor()), s), "expert choice by table")
+        _check(lib.sb_moe_sort(_p(idx), pairs, e, tile_rows, _p(offsets), _p(order), _p(tiles), _p(n_tiles), s), "grouping by expert")
+        act = torch.empty((pairs, ff), dtype=h.dtype, device=dev)
+        _check(lib.sb_moe_up(_p(h), h.stride(0), _p(w_up), _p(order), _p(offsets), _p(tiles), _p(n_tiles), _p(wts), top, pairs, e, k, ff,
+                             _p(act), _DT[h.dtype], s), "experts, up")
+        parts = out if top == 1 else torch.empty((pairs, n), dtype=torch.float32, device=dev)
+        _check(lib.sb_moe_down(_p(act), _p(w_down), _p(order), _p(offsets), _p(tiles), _p(n_tiles), _p(wts), pairs, e, ff, n, 1, _p(parts),
+                               _DT[h.dtype], _DT[parts.dtype], tile_rows, s), "experts, down")
         if top > 1:
             self.launches += 1
             _check(lib.sb_moe_combine(_p(parts), top, t, n, _p(out), _DT[out.dtype], s), "sum over a token's experts")
