@@ -11,7 +11,7 @@ of three: the way the reference's own benchmark times its generate()); ``prefill
 compares the decode step with the bytes it has to read (every weight once, and the cache of the live requests).
 The weights (2.47 GB) are larger than the L2 cache, so no flush is needed between steps.
 
-``--design rogisun`` is another measurement altogether and leaves the line above as it is: prefill and decode
+``--design rogisun`` (or ``bapavik``) is another measurement altogether and leaves the line above as it is: prefill and decode
 throughput of the Rogisun decoder (three layers, one of each mixer, routed experts) at layer sizes of real models,
 beside a Llama decoder of equal width, depth and active feed-forward size, each with the device time of every kernel
 of one prompt step and one decoding step; it prints its own JSON line (see design_bench).
@@ -351,6 +351,25 @@ def llama_at(width: int, vocab: int = 32000):
                              "rms_norm_eps": 1e-5, "rope_theta": 500000.0, "tie_word_embeddings": True, "max_position_embeddings": CONTEXT})
 
 
+def bapavik_at(width: int, vocab: int = 32000):
+    """A Bapavik configuration with layers of a real model's sizes: attention with heads of 128 and experts chosen by table,
+    latent attention (cached rows of 192 + 64, heads of 128 + 64) with experts, latent attention with a dense feed-forward."""
+    from serve_b200.config import config_from_dict
+
+    heads, experts, top, ff = DESIGN_SIZES[str(width)]
+    moe = {"kind": "moe", "expert": {"ff": ff}, "router": {"experts": experts, "top": top}}
+    att = {"heads": heads, "kv_heads": max(1, heads // 4), "dim": 128, "vdim": 128, "scale": 128 ** -0.5, "softcap": 50.0,
+           "q_temp": {"coef": 0.3, "every": 128}}
+    lat = {"heads": heads, "dim": 128, "rot_dim": 64, "vdim": 128, "kv_rank": 192, "scale": 192 ** -0.5, "rot": {"base": 10000.0, "dims": 64}}
+    layers = [{"type": "attention", "mixer": att, "mlp": moe}, {"type": "latent_attention", "mixer": lat, "mlp": moe},
+              {"type": "latent_attention", "mixer": lat, "mlp": {"kind": "dense", "ff": top * ff, "limit": 7.0}}]
+    return config_from_dict({"architecture": "Bapavik", "width": width, "vocab": vocab, "norm": {"eps": 1e-5}, "embedding": {"scale": 1.0},
+                             "layers": layers, "max_position": CONTEXT})
+
+
+DESIGNS = {"rogisun": rogisun_at, "bapavik": bapavik_at}
+
+
 def kernel_times(eng, entries, end):
     """Device time of every kernel of one step, added up by kernel name: [(name, launches, microseconds)], longest first."""
     import torch
@@ -394,8 +413,8 @@ def prefill_many(eng, vocab, requests, each, reps=5, seed=11):
 
 
 def design_bench(args):
-    """Prefill (one prompt of 2,048 tokens) and decode (batch 8 after 2,048-token prompts, from CUDA graphs) of Rogisun and of
-    the Llama decoder of equal size, at each width asked for, bfloat16, random weights; CUDA events on the stream, the
+    """Prefill (one prompt of 2,048 tokens) and decode (batch 8 after 2,048-token prompts, from CUDA graphs) of the named design
+    (Rogisun or Bapavik) and of the Llama decoder of equal size, at each width asked for, bfloat16, random weights; CUDA events on the stream, the
     weights alone exceed the L2 cache. Prints one JSON line: per width and design the two rates, the rate of a step of 8 prompts
     of 256 tokens (the same tokens side by side: what a recurrence walks in turn for one prompt it walks at once for eight),
     and the kernels of one prompt step and one (eager) decoding step with their device times."""
@@ -405,13 +424,13 @@ def design_bench(args):
     from serve_b200.engine import Engine, StepEntry
     from serve_b200.sampling import Sampler
 
-    out = {"design": "rogisun", "beside": "llama of equal width, depth and active feed-forward width", "dtype": "bf16",
+    out = {"design": args.design, "beside": "llama of equal width, depth and active feed-forward width", "dtype": "bf16",
            "data": "synthetic: uniform random token ids, seeded random weights", "prompt_tokens": PREFILL_TOKENS, "decode_batch": args.batch,
            "decode_context": PROMPT_LEN, "steps": args.steps, "warmup": max(args.warmup, 3), "sizes": {}}
     batch = args.batch
     for width in [int(w) for w in args.widths.split(",")]:
         rec = {}
-        for name, cfg in (("rogisun", rogisun_at(width)), ("llama", llama_at(width))):
+        for name, cfg in ((args.design, DESIGNS[args.design](width)), ("llama", llama_at(width))):
             ec = EngineConfig(dtype="bfloat16", page_size=64, num_pages=(batch + 2) * CONTEXT // 64, max_slots=batch + 2,
                               max_tokens_per_step=PREFILL_TOKENS, max_context=CONTEXT, use_cuda_graphs=not args.no_graphs)
             with torch.inference_mode():
@@ -447,7 +466,7 @@ def design_bench(args):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--design", default=None, choices=["rogisun"],
+    ap.add_argument("--design", default=None, choices=sorted(DESIGNS),
                     help="measure this design beside the Llama decoder of equal size instead of the headline workload")
     ap.add_argument("--widths", default="1024,2048,4096", help="with --design: layer widths to measure")
     ap.add_argument("--gpus", type=int, default=1)
