@@ -76,6 +76,7 @@ struct Params {
   float softcap_log2;    // > 0: a scaled score s becomes c * tanh(s / c), c the cap (kept here times log2 e), before any bias
   float softcap_in;      // scale / c: what the raw product is multiplied by inside the tanh
   const float* sinks;    // one per query head, or null: exp(sink) joins the softmax's denominator (no key, no value), once per row
+  int shared_kv;         // the value tensor is the key tensor (vc == kc): a tile is fetched once and read as both
   bf16* out;
   // deep shape only
   int split_size, num_splits;
@@ -196,8 +197,16 @@ __device__ __forceinline__ void load_kv_tile(const Params& p, const int* bt, int
       if (ok) off = (((size_t)page * p.Hkv + hk) * p.ps + (key - blk * p.ps)) * D + ch * 8;
     }
     cp_async16(Ks + row * LDS + ch * 8, p.kc + off, ok);
-    cp_async16(Vs + row * LDS + ch * 8, p.vc + off, ok);
+    if (!p.shared_kv) cp_async16(Vs + row * LDS + ch * 8, p.vc + off, ok);
   }
+}
+
+// The cap's tanh on the special-function unit, as the exponentials below (relative error about 2^-11, a quarter of what
+// rounding a query or key to bfloat16 does to the score; the float32 path uses tanhf).
+__device__ __forceinline__ float tanh_fast(float x) {
+  float y;
+  asm("tanh.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
 }
 
 // WM warps along rows, WN warps along the keys of a tile (WM * WN == 4).
@@ -283,7 +292,7 @@ __global__ void __launch_bounds__(THREADS, (D <= 64 ? 4 : 1)) attention_wide_ker
   for (int it = 0; it < n_tiles; ++it) {
     const int kt = kt0 + it * BN;
     bf16* Ks = KVs + (it & 1) * 2 * BN * LDS;
-    bf16* Vs = Ks + BN * LDS;
+    bf16* Vs = p.shared_kv ? Ks : Ks + BN * LDS;
     if (it + 1 < n_tiles) {
       bf16* Kn = KVs + ((it + 1) & 1) * 2 * BN * LDS;
       load_kv_tile(p, bt, bt_first, hk, kt + BN, lo, hi, Kn, Kn + BN * LDS);
@@ -335,8 +344,8 @@ __global__ void __launch_bounds__(THREADS, (D <= 64 ? 4 : 1)) attention_wide_ker
           const bool in_range = key >= lo && key < hi;
           const bool ok_a = in_range && key <= pos_a && key >= first_a && (p.window <= 0 || key > pos_a - p.window);
           const bool ok_b = in_range && key <= pos_b && key >= first_b && (p.window <= 0 || key > pos_b - p.window);
-          const float va = capped ? p.softcap_log2 * tanhf(s[j][e] * p.softcap_in) : s[j][e] * p.scale_log2;
-          const float vb = capped ? p.softcap_log2 * tanhf(s[j][2 + e] * p.softcap_in) : s[j][2 + e] * p.scale_log2;
+          const float va = capped ? p.softcap_log2 * tanh_fast(s[j][e] * p.softcap_in) : s[j][e] * p.scale_log2;
+          const float vb = capped ? p.softcap_log2 * tanh_fast(s[j][2 + e] * p.softcap_in) : s[j][2 + e] * p.scale_log2;
           s[j][e] = ok_a ? va - slope_a * (float)(pos_a - key) : -INFINITY;
           s[j][2 + e] = ok_b ? vb - slope_b * (float)(pos_b - key) : -INFINITY;
           mx_a = fmaxf(mx_a, s[j][e]);
@@ -445,7 +454,7 @@ __device__ __forceinline__ void load_kv_subtile(const Params& p, const int* bt, 
       const int row = c / CHUNKS, ch = c - row * CHUNKS;
       const bool ok = inner || (page_ok && k0 + row >= lo && k0 + row < hi);
       cp_async16(Ks + row * LDS + ch * 8, p.kc + base + (size_t)c * 8, ok);
-      cp_async16(Vs + row * LDS + ch * 8, p.vc + base + (size_t)c * 8, ok);
+      if (!p.shared_kv) cp_async16(Vs + row * LDS + ch * 8, p.vc + base + (size_t)c * 8, ok);
     }
     return;
   }
@@ -465,7 +474,7 @@ __device__ __forceinline__ void load_kv_subtile(const Params& p, const int* bt, 
       const bool ok = (second ? ok_b : ok_a) && (inner || (k0 + row >= lo && k0 + row < hi));
       const size_t off = (second ? base_b : base_a) + (size_t)(row & 15) * D + ch * 8;
       cp_async16(Ks + row * LDS + ch * 8, p.kc + off, ok);
-      cp_async16(Vs + row * LDS + ch * 8, p.vc + off, ok);
+      if (!p.shared_kv) cp_async16(Vs + row * LDS + ch * 8, p.vc + off, ok);
     }
     return;
   }
@@ -483,7 +492,7 @@ __device__ __forceinline__ void load_kv_subtile(const Params& p, const int* bt, 
       if (ok) off = (((size_t)page * p.Hkv + hk) * p.ps + (key - blk * p.ps)) * D + ch * 8;
     }
     cp_async16(Ks + row * LDS + ch * 8, p.kc + off, ok);
-    cp_async16(Vs + row * LDS + ch * 8, p.vc + off, ok);
+    if (!p.shared_kv) cp_async16(Vs + row * LDS + ch * 8, p.vc + off, ok);
   }
 }
 
@@ -610,7 +619,7 @@ __global__ void __launch_bounds__(NWARPS * 32) attention_deep_kernel(const Param
     }
     __syncwarp();
     const bf16* Ks = myKV + (it % DSTAGES) * 2 * DKW * LDS;
-    const bf16* Vs = Ks + DKW * LDS;
+    const bf16* Vs = p.shared_kv ? Ks : Ks + DKW * LDS;
     const int kbase = k_first + (warp + NWARPS * it) * DKW;
     float s[DNT][4];
 #pragma unroll
@@ -652,12 +661,12 @@ __global__ void __launch_bounds__(NWARPS * 32) attention_deep_kernel(const Param
           const int key = kbase + j * 8 + tq * 2 + e;
           const bool in_range = key >= lo && key < hi;
           const bool ok_a = in_range && key <= pos_a && key >= first_a && (p.window <= 0 || key > pos_a - p.window);
-          const float va = capped ? p.softcap_log2 * tanhf(s[j][e] * p.softcap_in) : s[j][e] * p.scale_log2;
+          const float va = capped ? p.softcap_log2 * tanh_fast(s[j][e] * p.softcap_in) : s[j][e] * p.scale_log2;
           s[j][e] = ok_a ? va - slope_a * (float)(pos_a - key) : -INFINITY;
           mx_a = fmaxf(mx_a, s[j][e]);
           if (UPPER) {
             const bool ok_b = in_range && key <= pos_b && key >= first_b && (p.window <= 0 || key > pos_b - p.window);
-            const float vb = capped ? p.softcap_log2 * tanhf(s[j][2 + e] * p.softcap_in) : s[j][2 + e] * p.scale_log2;
+            const float vb = capped ? p.softcap_log2 * tanh_fast(s[j][2 + e] * p.softcap_in) : s[j][2 + e] * p.scale_log2;
             s[j][2 + e] = ok_b ? vb - slope_b * (float)(pos_b - key) : -INFINITY;
             mx_b = fmaxf(mx_b, s[j][2 + e]);
           }
@@ -827,7 +836,7 @@ SB_EXPORT int sb_attention_mma_opts(const void* qkv, int q_stride, const void* k
   p.H = H; p.Hkv = Hkv; p.G = H / Hkv; p.ps = ps; p.num_pages = num_pages;
   p.ps_shift = (ps & (ps - 1)) == 0 ? __builtin_ctz((unsigned)ps) : -1;
   p.scale_log2 = scale * LOG2E; p.window = window; p.out = (bf16*)out; p.slopes = slopes; p.chunk = chunk;
-  p.softcap_log2 = softcap > 0.f ? softcap * LOG2E : 0.f; p.softcap_in = softcap > 0.f ? scale / softcap : 0.f; p.sinks = sinks;
+  p.softcap_log2 = softcap > 0.f ? softcap * LOG2E : 0.f; p.softcap_in = softcap > 0.f ? scale / softcap : 0.f; p.sinks = sinks; p.shared_kv = (kc == vc) ? 1 : 0;
   p.split_size = 0; p.num_splits = num_splits; p.part_o = nullptr; p.part_ml = nullptr; p.tickets = nullptr;
   p.wide_rows = wide_rows; p.heads_in_x = 0;
   if (which & 1) {
@@ -967,7 +976,7 @@ SB_EXPORT int sb_attention_decode_noalloc(const void* qkv, int q_stride, const v
   p.H = H; p.Hkv = Hkv; p.G = G; p.ps = ps; p.num_pages = num_pages;
   p.ps_shift = (ps & (ps - 1)) == 0 ? __builtin_ctz((unsigned)ps) : -1;
   p.scale_log2 = scale * LOG2E; p.window = window; p.out = (bf16*)out; p.slopes = nullptr; p.chunk = 0;
-  p.softcap_log2 = 0.f; p.softcap_in = 0.f; p.sinks = nullptr;
+  p.softcap_log2 = 0.f; p.softcap_in = 0.f; p.sinks = nullptr; p.shared_kv = (kc == vc) ? 1 : 0;
   p.split_size = 0; p.num_splits = num_splits; p.part_o = nullptr; p.part_ml = nullptr; p.tickets = nullptr;
   p.wide_rows = nullptr;
   if (num_splits > 1) {

@@ -113,7 +113,19 @@ struct RopeEpilogue {
   bf16* vc;
   int* errors;
   int rot, H, Hkv, D, bt_width, ps, num_pages, write_cache;
+  // gate/up epilogue: limit > 0 asks for the clamped activation g <- min(g, limit), u <- clamp(u, -limit, limit),
+  // g * sigmoid(alpha g) * (u + 1) in place of silu(g) * u
+  float act_limit, act_alpha;
 };
+
+__device__ __forceinline__ float gated_act(float g, float u, float limit, float alpha) {
+  if (limit > 0.f) {
+    g = fminf(g, limit);
+    u = fminf(fmaxf(u, -limit), limit);
+    return g / (1.0f + expf(-alpha * g)) * (u + 1.0f);
+  }
+  return g / (1.0f + expf(-g)) * u;
+}
 
 // Where the keys and values of this thread's row go: element offset of (page, kv head 0, slot, 0) or -1.
 __device__ __forceinline__ long long rope_row_slot(const RopeEpilogue& ra, int row, int pos) {
@@ -302,7 +314,7 @@ __global__ void __launch_bounds__(THREADS) gemm_tcgen05_kernel(const __grid_cons
             // both halves rounded to the activation type first, as the unfused path stores them
             const float g0 = to_float(__float2bfloat16_rn(__uint_as_float(v[2 * i]))), g1 = to_float(__float2bfloat16_rn(__uint_as_float(v[2 * i + 1])));
             const float u0 = to_float(__float2bfloat16_rn(__uint_as_float(u[2 * i]))), u1 = to_float(__float2bfloat16_rn(__uint_as_float(u[2 * i + 1])));
-            __nv_bfloat162 o = __floats2bfloat162_rn(g0 / (1.0f + expf(-g0)) * u0, g1 / (1.0f + expf(-g1)) * u1);
+            __nv_bfloat162 o = __floats2bfloat162_rn(gated_act(g0, u0, ra.act_limit, ra.act_alpha), gated_act(g1, u1, ra.act_limit, ra.act_alpha));
             packed[i] = *reinterpret_cast<uint32_t*>(&o);
           }
         } else {
@@ -505,7 +517,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS)
           for (int i = 0; i < 16; ++i) {
             const float g0 = to_float(__float2bfloat16_rn(__uint_as_float(v[2 * i]))), g1 = to_float(__float2bfloat16_rn(__uint_as_float(v[2 * i + 1])));
             const float u0 = to_float(__float2bfloat16_rn(__uint_as_float(u[2 * i]))), u1 = to_float(__float2bfloat16_rn(__uint_as_float(u[2 * i + 1])));
-            __nv_bfloat162 o = __floats2bfloat162_rn(g0 / (1.0f + expf(-g0)) * u0, g1 / (1.0f + expf(-g1)) * u1);
+            __nv_bfloat162 o = __floats2bfloat162_rn(gated_act(g0, u0, ra.act_limit, ra.act_alpha), gated_act(g1, u1, ra.act_limit, ra.act_alpha));
             packed[i] = *reinterpret_cast<uint32_t*>(&o);
           }
         } else {
@@ -691,6 +703,15 @@ SB_EXPORT int sb_gemm_tcgen05_pair_capacity(int gate_up) { return pair_capacity(
 
 // 1 if sb_gemm_tcgen05 takes these sizes (else the caller uses the library product).
 SB_EXPORT int sb_gemm_tcgen05_supports(int M, int N, int K, int gate_up) { return supports(M, N, K, gate_up ? EPI_GATE_UP : EPI_STORE); }
+
+// The gate/up product with the clamped activation in its epilogue (see RopeEpilogue): w [2N, K], out [M, N].
+SB_EXPORT int sb_gemm_tcgen05_gate_up_clamped(const void* a, const void* w, void* out, int M, int N, int K, float limit, float alpha,
+                                              int* error, cudaStream_t stream) {
+  if (!(limit > 0.f)) return SB_ERR_SHAPE;
+  RopeEpilogue ra{};
+  ra.act_limit = limit; ra.act_alpha = alpha;
+  return run_product(a, w, out, M, N, K, EPI_GATE_UP, ra, error, stream);
+}
 
 // error: device int set to 1 if a bounded wait inside the kernel ran out.
 SB_EXPORT int sb_gemm_tcgen05(const void* a, const void* w, void* out, int M, int N, int K, int gate_up, int* error,

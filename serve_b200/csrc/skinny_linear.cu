@@ -51,6 +51,9 @@ struct RopeArgs {
   int bt_width, ps, num_pages, write_cache;
   int* errors;
   int late_trigger;    // let the kernel after this one start only when this kernel's products are done (see launch_mt)
+  // gate/up products: limit > 0 asks for the clamped activation g <- min(g, limit), u <- clamp(u, -limit, limit),
+  // g * sigmoid(alpha g) * (u + 1) in place of silu(g) * u
+  float act_limit, act_alpha;
 };
 
 // MT: tiles of 16 activation rows (M <= 16*MT); HALF: only rows 0..7 of the single tile exist (M <= 8).
@@ -181,7 +184,12 @@ __global__ void __launch_bounds__(THREADS, 2) skinny_linear_kernel(const bf16* _
     if (GU) {
       // both halves are rounded to the activation type first, as if the [M, 2N] intermediate had been stored
       const float gte = to_float(__float2bfloat16_rn(s0)), up = to_float(__float2bfloat16_rn(s1));
-      v = gte / (1.0f + expf(-gte)) * up;
+      if (ra.act_limit > 0.f) {
+        const float gc = fminf(gte, ra.act_limit), uc = fminf(fmaxf(up, -ra.act_limit), ra.act_limit);
+        v = gc / (1.0f + expf(-ra.act_alpha * gc)) * (uc + 1.0f);
+      } else {
+        v = gte / (1.0f + expf(-gte)) * up;
+      }
     }
     if (ROPE) {
       const int head = n / ra.D, i = n - head * ra.D;
@@ -233,8 +241,10 @@ inline bool wide_blocks(int N) {
 }
 
 template <bool GU, typename OutT>
-int launch_mt(const void* a, const void* w, void* out, int M, int N, int K, cudaStream_t stream) {
+int launch_mt(const void* a, const void* w, void* out, int M, int N, int K, cudaStream_t stream, float act_limit = 0.f,
+              float act_alpha = 1.f) {
   RopeArgs none = {};
+  none.act_limit = act_limit; none.act_alpha = act_alpha;
   // A plain product with bfloat16 output is followed by the add + norm kernel (a handful of blocks). If that kernel
   // is launched ahead, it should come in when this kernel's products are done, not when they start: it would release
   // its own successor at once, and blocks of kernels two and three launches ahead would take the places of running ones.
@@ -371,6 +381,14 @@ SB_EXPORT int sb_skinny_linear_supports(int M, int N, int K, int gate_up) {
   return 1;
 }
 
+// The gate/up product with the clamped activation in its epilogue (see RopeArgs): w [2N, K], out [M, N] bf16.
+SB_EXPORT int sb_skinny_gate_up_clamped(const void* a, const void* w, void* out, int M, int N, int K, float limit, float alpha,
+                                        cudaStream_t stream) {
+  if (!sb_skinny_linear_supports(M, N, K, 1) || !(limit > 0.f)) return SB_ERR_SHAPE;
+  if (!aligned16(a) || !aligned16(w)) return SB_ERR_ALIGN;
+  return launch_mt<true, bf16>(a, w, out, M, N, K, stream, limit, alpha);
+}
+
 // a [M,K] bf16, w [N,K] bf16 (or [2N,K] with gate_up), out [M,N] bf16 (out_dtype 1) or float (0).
 SB_EXPORT int sb_skinny_linear(const void* a, const void* w, void* out, int M, int N, int K, int out_dtype, int gate_up,
                                cudaStream_t stream) {
@@ -398,7 +416,7 @@ SB_EXPORT int sb_skinny_qkv_rope(const void* a, const void* w, void* out, int M,
   RopeArgs ra;
   ra.positions = positions; ra.token_row = token_row; ra.inv_freq = inv_freq; ra.rot = rot; ra.H = H; ra.Hkv = Hkv; ra.D = D;
   ra.kc = (bf16*)kc; ra.vc = (bf16*)vc; ra.block_table = block_table; ra.bt_width = bt_width; ra.ps = ps; ra.num_pages = num_pages;
-  ra.write_cache = write_cache; ra.errors = errors; ra.late_trigger = 0;
+  ra.write_cache = write_cache; ra.errors = errors; ra.late_trigger = 0; ra.act_limit = 0.f; ra.act_alpha = 1.f;
   const bool wide = wide_blocks(N);
   if (M <= 8) {
     if (wide) return launch<1, true, 2, false, true, bf16>(a, w, out, M, N, K, ra, stream);

@@ -315,6 +315,20 @@ class CudaKernels:
         t, inter = h.shape[0], out.shape[1]
         if w_gate_up.shape[0] != 2 * inter or w_gate_up.shape[1] != h.shape[1] or out.shape[0] != t:
             raise KernelError("gate_up_activation: shapes do not fit")
+        k = h.shape[1]
+        if h.dtype == torch.bfloat16 and out.dtype == torch.bfloat16 and activation == "clamped_swish" and limit > 0.0:
+            # the same two fused products as gate_up_swiglu, with the other activation in their epilogues
+            if self.use_skinny_linear and self._core.sb_skinny_linear_supports(t, inter, k, 1):
+                self.launches += 1
+                _check(self._core.sb_skinny_gate_up_clamped(_p(h), _p(w_gate_up), _p(out), t, inter, k, ctypes.c_float(limit),
+                                                            ctypes.c_float(alpha), self._s()), "skinny gate/up, clamped")
+                return
+            if self._tcgen05_worthwhile(t, 2 * inter) and self._core.sb_gemm_tcgen05_supports(t, inter, k, 1):
+                self.launches += 1
+                _check(self._core.sb_gemm_tcgen05_gate_up_clamped(_p(h), _p(w_gate_up), _p(out), t, inter, k, ctypes.c_float(limit),
+                                                                  ctypes.c_float(alpha), self._wait_flag(), self._s()),
+                       "tcgen05 gate/up, clamped")
+                return
         gate_up = torch.empty((t, 2 * inter), dtype=h.dtype, device=h.device)
         self.linear(h, w_gate_up, gate_up)
         self.launches += 1
@@ -503,11 +517,13 @@ class CudaKernels:
     TARGET_BLOCKS = 148
     MAX_SPLITS = 32
 
-    def split_plan(self, rows: int, kv_heads: int, max_kv: int) -> int:
+    def split_plan(self, rows: int, kv_heads: int, max_kv: int, keys_per_split: int = 256) -> int:
         """Number of key splits of the deep shape for a batch; a function of sizes only, never of data.
-        (Each request's own length is then shared out evenly over the splits inside the kernel.)"""
+        (Each request's own length is then shared out evenly over the splits inside the kernel.) ``keys_per_split``: no split
+        gets fewer keys than this; 256 as a rule, 128 where all query heads share one cached row per token (so a request is
+        one (request, kv head) pair and a batch of 8 would otherwise fill 64 of the SMs)."""
         want = max(1, self.TARGET_BLOCKS // max(1, rows * kv_heads))
-        return max(1, min(want, -(-max_kv // 256), self.MAX_SPLITS))
+        return max(1, min(want, -(-max_kv // keys_per_split), self.MAX_SPLITS))
 
     def _attention_mma(self, lib, qkv, k_cache, v_cache, block_table, cu_q, kv_len, heads, kv_heads, head_dim, page_size,
                        scale, window, out, shape, slopes=None, chunk: int = 0, softcap: float = 0.0, sinks=None) -> None:
@@ -533,7 +549,7 @@ class CudaKernels:
             wide_rows = shape.rows_by_q
         num_splits, scratch, tickets = 1, None, None
         if which & 2:
-            num_splits = self.split_plan(shape.rows, kv_heads, shape.max_kv)
+            num_splits = self.split_plan(shape.rows, kv_heads, shape.max_kv, 128 if k_cache is v_cache else 256)
             if num_splits > 1:
                 scratch = self._scratch_buffer(lib, shape.rows, kv_heads, num_splits)
                 tickets = self._ticket_buffer(shape.rows * kv_heads)

@@ -583,3 +583,22 @@ def test_trace_run_and_command_line_programs(models, tmp_path):
     new = json.loads([l for l in out.stdout.splitlines() if l.startswith("{")][-1])["generated_tokens"]
     logits = plain_logits(w, CONFIGS["a"], prompt + new)
     assert all(int(logits[len(prompt) - 1 + i].argmax()) == t for i, t in enumerate(new))
+
+
+@pytest.mark.parametrize("backend", BACKENDS[1:])
+@pytest.mark.parametrize("rows", [5, 16, 300, 2048])
+def test_dense_feed_forward_at_the_sizes_of_a_real_layer(backend, rows):
+    """Width 512 and 2,048 inner columns: a handful of rows take the few-rows product, thousands the tensor-memory tiles (both
+    with the activation in their epilogue, in bfloat16), the row counts between them the library product and the activation
+    kernel; all three must give the same numbers."""
+    width, ff, limit = 512, 2048, 1.25
+    g = torch.Generator().manual_seed(rows)
+    rnd = lambda *shape, s=1.0: (torch.randn(*shape, generator=g) * s).bfloat16().float()
+    w = {"f.gate": rnd(ff, width, s=2.0 * width ** -0.5), "f.up": rnd(ff, width, s=2.0 * width ** -0.5), "f.down": rnd(width, ff, s=ff ** -0.5)}
+    x = rnd(rows, width)
+    f = {"kind": "dense", "ff": ff, "limit": limit}
+    want = P.dense_feed_forward(x.double(), {k: v.double() for k, v in w.items()}, "f.", f).float()
+    spec = PartSpec("gated_dense", {"hidden": width, "intermediate": ff, "activation": "clamped_swish", "limit": limit, "alpha": 1.702,
+                                    "names": {"gate": "gate", "up": "up", "down": "down"}}, "f.")
+    got = _run_part(backend, "feed_forward", spec, w, x, [rows], page=64, pages=64)
+    torch.testing.assert_close(got, want, atol=_tol(backend, want), rtol=0)
