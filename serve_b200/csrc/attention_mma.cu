@@ -77,6 +77,10 @@ struct Params {
   float softcap_in;      // scale / c: what the raw product is multiplied by inside the tanh
   const float* sinks;    // one per query head, or null: exp(sink) joins the softmax's denominator (no key, no value), once per row
   int shared_kv;         // the value tensor is the key tensor (vc == kc): a tile is fetched once and read as both
+  // The cache holds cache_Hkv heads; Hkv above may be kv_div times as many: the query heads of one cached head are then
+  // dealt to kv_div groups of G that read the same cached rows (kv head hk reads cached head hk / kv_div). A cached head
+  // shared by many query heads thus gives several (request, kv head) pairs, each with few rows, for the SMs to share.
+  int cache_Hkv, kv_div;
   bf16* out;
   // deep shape only
   int split_size, num_splits;
@@ -194,7 +198,7 @@ __device__ __forceinline__ void load_kv_tile(const Params& p, const int* bt, int
       const int blk = p.ps_shift >= 0 ? (key >> p.ps_shift) : key / p.ps;
       const int page = blk < p.bt_width ? bt[blk - bt_first] : -1;
       ok = page >= 0 && page < p.num_pages;
-      if (ok) off = (((size_t)page * p.Hkv + hk) * p.ps + (key - blk * p.ps)) * D + ch * 8;
+      if (ok) off = (((size_t)page * p.cache_Hkv + hk / p.kv_div) * p.ps + (key - blk * p.ps)) * D + ch * 8;
     }
     cp_async16(Ks + row * LDS + ch * 8, p.kc + off, ok);
     if (!p.shared_kv) cp_async16(Vs + row * LDS + ch * 8, p.vc + off, ok);
@@ -446,7 +450,7 @@ __device__ __forceinline__ void load_kv_subtile(const Params& p, const int* bt, 
     const int blk = p.ps_shift >= 0 ? (k0 >> p.ps_shift) : k0 / p.ps;
     const int page = blk < p.bt_width ? bt[blk - bt_first] : -1;
     const bool page_ok = page >= 0 && page < p.num_pages;
-    const size_t base = (((size_t)(page_ok ? page : 0) * p.Hkv + hk) * p.ps + (k0 - blk * p.ps)) * D;
+    const size_t base = (((size_t)(page_ok ? page : 0) * p.cache_Hkv + hk / p.kv_div) * p.ps + (k0 - blk * p.ps)) * D;
     const bool inner = page_ok && k0 >= lo && k0 + DKW <= hi;
 #pragma unroll
     for (int i = 0; i < DCOPIES; ++i) {
@@ -464,7 +468,7 @@ __device__ __forceinline__ void load_kv_subtile(const Params& p, const int* bt, 
     const int blk = k0 >> 4;
     const int page_a = blk < p.bt_width ? bt[blk - bt_first] : -1, page_b = blk + 1 < p.bt_width ? bt[blk + 1 - bt_first] : -1;
     const bool ok_a = page_a >= 0 && page_a < p.num_pages, ok_b = page_b >= 0 && page_b < p.num_pages;
-    const size_t base_a = ((size_t)(ok_a ? page_a : 0) * p.Hkv + hk) * 16 * D, base_b = ((size_t)(ok_b ? page_b : 0) * p.Hkv + hk) * 16 * D;
+    const size_t base_a = ((size_t)(ok_a ? page_a : 0) * p.cache_Hkv + hk / p.kv_div) * 16 * D, base_b = ((size_t)(ok_b ? page_b : 0) * p.cache_Hkv + hk / p.kv_div) * 16 * D;
     const bool inner = k0 >= lo && k0 + DKW <= hi;
 #pragma unroll
     for (int i = 0; i < DCOPIES; ++i) {
@@ -489,7 +493,7 @@ __device__ __forceinline__ void load_kv_subtile(const Params& p, const int* bt, 
       const int blk = p.ps_shift >= 0 ? (key >> p.ps_shift) : key / p.ps;
       const int page = blk < p.bt_width ? bt[blk - bt_first] : -1;
       ok = page >= 0 && page < p.num_pages;
-      if (ok) off = (((size_t)page * p.Hkv + hk) * p.ps + (key - blk * p.ps)) * D + ch * 8;
+      if (ok) off = (((size_t)page * p.cache_Hkv + hk / p.kv_div) * p.ps + (key - blk * p.ps)) * D + ch * 8;
     }
     cp_async16(Ks + row * LDS + ch * 8, p.kc + off, ok);
     if (!p.shared_kv) cp_async16(Vs + row * LDS + ch * 8, p.vc + off, ok);
@@ -825,12 +829,15 @@ SB_EXPORT int sb_attention_mma_opts(const void* qkv, int q_stride, const void* k
                                     const int* cu_q, const int* kv_len, int H, int Hkv, int ps, int num_pages, float scale, int window,
                                     void* out, int n_rows, int max_q, int which, int longest, int num_splits, void* scratch,
                                     int* tickets, const int* wide_rows, int n_wide, const float* slopes, int chunk, float softcap,
-                                    const float* sinks, cudaStream_t stream) {
+                                    const float* sinks, int kv_div, cudaStream_t stream) {
   if (n_rows <= 0 || max_q <= 0) return 0;
   if (H <= 0 || Hkv <= 0 || H % Hkv || ps <= 0 || bt_width <= 0) return SB_ERR_SHAPE;
+  // Hkv counts the groups of query heads; the cache has Hkv / kv_div heads (kv_div 1: the usual case)
+  if (kv_div < 1 || Hkv % kv_div) return SB_ERR_SHAPE;
   if (Hkv > 65535 || n_rows > 65535) return SB_ERR_LIMIT;
   if ((q_stride % 8) || !aligned16(qkv) || !aligned16(kc) || !aligned16(vc) || !aligned16(out)) return SB_ERR_ALIGN;
   Params p;
+  p.cache_Hkv = Hkv / kv_div; p.kv_div = kv_div;
   p.qkv = (const bf16*)qkv; p.q_stride = q_stride; p.kc = (const bf16*)kc; p.vc = (const bf16*)vc;
   p.block_table = block_table; p.bt_width = bt_width; p.cu_q = cu_q; p.kv_len = kv_len;
   p.H = H; p.Hkv = Hkv; p.G = H / Hkv; p.ps = ps; p.num_pages = num_pages;
@@ -930,7 +937,7 @@ SB_EXPORT int sb_attention_mma_biased(const void* qkv, int q_stride, const void*
                                       cudaStream_t stream) {
   return sb_attention_mma_opts(qkv, q_stride, kc, vc, block_table, bt_width, cu_q, kv_len, H, Hkv, ps, num_pages, scale, window, out,
                                n_rows, max_q, which, longest, num_splits, scratch, tickets, wide_rows, n_wide, slopes, chunk, 0.f, nullptr,
-                               stream);
+                               1, stream);
 }
 
 SB_EXPORT int sb_attention_mma(const void* qkv, int q_stride, const void* kc, const void* vc, const int* block_table, int bt_width,
@@ -976,7 +983,7 @@ SB_EXPORT int sb_attention_decode_noalloc(const void* qkv, int q_stride, const v
   p.H = H; p.Hkv = Hkv; p.G = G; p.ps = ps; p.num_pages = num_pages;
   p.ps_shift = (ps & (ps - 1)) == 0 ? __builtin_ctz((unsigned)ps) : -1;
   p.scale_log2 = scale * LOG2E; p.window = window; p.out = (bf16*)out; p.slopes = nullptr; p.chunk = 0;
-  p.softcap_log2 = 0.f; p.softcap_in = 0.f; p.sinks = nullptr; p.shared_kv = (kc == vc) ? 1 : 0;
+  p.softcap_log2 = 0.f; p.softcap_in = 0.f; p.sinks = nullptr; p.shared_kv = (kc == vc) ? 1 : 0; p.cache_Hkv = Hkv; p.kv_div = 1;
   p.split_size = 0; p.num_splits = num_splits; p.part_o = nullptr; p.part_ml = nullptr; p.tickets = nullptr;
   p.wide_rows = nullptr;
   if (num_splits > 1) {

@@ -516,17 +516,25 @@ class CudaKernels:
     # SM count when the kernels are loaded; 148 on a B200).
     TARGET_BLOCKS = 148
     MAX_SPLITS = 32
+    # query heads per group when all heads share one cached row per token (SERVE_B200_LATENT_GROUP for measurements)
+    LATENT_GROUP = int(os.environ.get("SERVE_B200_LATENT_GROUP", "8"))
 
-    def split_plan(self, rows: int, kv_heads: int, max_kv: int, keys_per_split: int = 256) -> int:
+    def split_plan(self, rows: int, kv_heads: int, max_kv: int) -> int:
         """Number of key splits of the deep shape for a batch; a function of sizes only, never of data.
-        (Each request's own length is then shared out evenly over the splits inside the kernel.) ``keys_per_split``: no split
-        gets fewer keys than this; 256 as a rule, 128 where all query heads share one cached row per token (so a request is
-        one (request, kv head) pair and a batch of 8 would otherwise fill 64 of the SMs)."""
+        (Each request's own length is then shared out evenly over the splits inside the kernel.)"""
         want = max(1, self.TARGET_BLOCKS // max(1, rows * kv_heads))
-        return max(1, min(want, -(-max_kv // keys_per_split), self.MAX_SPLITS))
+        return max(1, min(want, -(-max_kv // 256), self.MAX_SPLITS))
 
     def _attention_mma(self, lib, qkv, k_cache, v_cache, block_table, cu_q, kv_len, heads, kv_heads, head_dim, page_size,
                        scale, window, out, shape, slopes=None, chunk: int = 0, softcap: float = 0.0, sinks=None) -> None:
+        # One cached row for many query heads (keys and values the same tensor): the heads are dealt to groups of LATENT_GROUP
+        # that each count as a kv head reading the same rows. A decoding request is then several (request, kv head) pairs of
+        # few rows, which the deep shape spreads over the SMs with its key splits; as one pair of 32 rows it would be a single
+        # block of the wide shape walking all keys alone. For prompt portions the grouping changes neither work nor traffic.
+        kv_div = 1
+        if k_cache is v_cache and kv_heads * self.LATENT_GROUP < heads and heads % (kv_heads * self.LATENT_GROUP) == 0:
+            kv_div = heads // (kv_heads * self.LATENT_GROUP)
+            kv_heads = kv_heads * kv_div
         group = heads // kv_heads
         min_q = getattr(shape, "min_q", 1)
         which = 0
@@ -549,12 +557,12 @@ class CudaKernels:
             wide_rows = shape.rows_by_q
         num_splits, scratch, tickets = 1, None, None
         if which & 2:
-            num_splits = self.split_plan(shape.rows, kv_heads, shape.max_kv, 128 if k_cache is v_cache else 256)
+            num_splits = self.split_plan(shape.rows, kv_heads, shape.max_kv)
             if num_splits > 1:
                 scratch = self._scratch_buffer(lib, shape.rows, kv_heads, num_splits)
                 tickets = self._ticket_buffer(shape.rows * kv_heads)
         by_distance = slopes is not None or chunk > 0 or softcap > 0.0 or sinks is not None
-        if (which & 1) and not by_distance and self.use_tcgen05_attention and self._tc_attention_takes(lib, heads, kv_heads, head_dim, page_size, window, qkv.shape[1]):
+        if (which & 1) and not by_distance and kv_div == 1 and self.use_tcgen05_attention and self._tc_attention_takes(lib, heads, kv_heads, head_dim, page_size, window, qkv.shape[1]):
             # prompt portions on the tensor-memory path; what is left (decoding rows) goes to the deep shape below
             self.launches += 1
             _check(lib.sb_attention_tc(
@@ -570,7 +578,7 @@ class CudaKernels:
             _p(qkv), qkv.stride(0), _p(k_cache), _p(v_cache), _p(block_table), block_table.shape[1], _p(cu_q), _p(kv_len),
             heads, kv_heads, page_size, k_cache.shape[0], ctypes.c_float(scale), window, _p(out), shape.rows, shape.max_q,
             which, int(shape.max_kv), num_splits, _p(scratch), _p(tickets), _p(wide_rows), n_wide, _p(slopes), chunk,
-            ctypes.c_float(softcap), _p(sinks), self._s()), "attention")
+            ctypes.c_float(softcap), _p(sinks), kv_div, self._s()), "attention")
 
     def _tc_attention_takes(self, lib, heads, kv_heads, head_dim, page_size, window, stride) -> bool:
         key = (heads, kv_heads, head_dim, page_size, window, stride)

@@ -602,3 +602,31 @@ def test_dense_feed_forward_at_the_sizes_of_a_real_layer(backend, rows):
                                     "names": {"gate": "gate", "up": "up", "down": "down"}}, "f.")
     got = _run_part(backend, "feed_forward", spec, w, x, [rows], page=64, pages=64)
     torch.testing.assert_close(got, want, atol=_tol(backend, want), rtol=0)
+
+
+@pytest.mark.parametrize("backend", BACKENDS[2:])
+@pytest.mark.parametrize("heads,group", [(16, 8), (32, 8), (24, 8), (8, 4), (12, 8)])
+def test_latent_attention_with_many_heads_in_groups(backend, heads, group):
+    """All heads read one cached row per token; the bfloat16 kernels deal them to groups that each count as a key/value
+    head of their own (12 heads do not divide into groups of 8 and stay one group). Prompt, portions and decoded tokens
+    after 700 cached ones, where the keys are also split over blocks."""
+    from serve_b200.models.bapavik import _mixer_spec
+
+    m = {"heads": heads, "dim": 32, "rot_dim": 16, "vdim": 32, "kv_rank": 48, "scale": 0.15, "rot": {"base": 10000.0, "dims": 16}}
+    width = 128
+    g = torch.Generator().manual_seed(heads)
+    rnd = lambda *shape: (torch.randn(*shape, generator=g) * 1.5 / shape[-1] ** 0.5).bfloat16().float()
+    w = {"t.q": rnd(heads * 48, width), "t.dkv": rnd(64, width), "t.dkv.norm": (1 + 0.2 * torch.randn(48, generator=g)).bfloat16().float(),
+         "t.uk": rnd(heads * 32, 48), "t.uv": rnd(heads * 32, 48), "t.o": rnd(width, heads * 32)}
+    x = torch.randn(730, width, generator=g).bfloat16().float()
+    want = P.latent_attention(x.double(), {k: v.double() for k, v in w.items()}, "t.", m, 1e-5).float()
+    spec = _mixer_spec("latent_attention", m, width, 1e-5, "t.")
+    rt, _ = runtime_for(backend)
+    before = rt.kernels.LATENT_GROUP
+    rt.kernels.LATENT_GROUP = group
+    try:
+        for cuts in ([730], [700, 3, 2] + [1] * 25):
+            got = _run_part(backend, "mixer", spec, w, x, cuts, page=16)
+            torch.testing.assert_close(got, want, atol=_tol(backend, want), rtol=0)
+    finally:
+        rt.kernels.LATENT_GROUP = before
