@@ -188,6 +188,7 @@ constexpr int BT_CACHE = 256;        // block-table entries a thread block keeps
 // bt points at the table entry of block bt_first (shared memory copy, or the table itself with bt_first 0).
 __device__ __forceinline__ void load_kv_tile(const Params& p, const int* bt, int bt_first, int hk, int kt, int lo, int hi, bf16* Ks,
                                              bf16* Vs) {
+  const int hkc = hk / p.kv_div;                 // the cached head this group of query heads reads
 #pragma unroll
   for (int idx = threadIdx.x; idx < BN * CHUNKS; idx += THREADS) {
     const int row = idx / CHUNKS, ch = idx - row * CHUNKS;
@@ -198,7 +199,7 @@ __device__ __forceinline__ void load_kv_tile(const Params& p, const int* bt, int
       const int blk = p.ps_shift >= 0 ? (key >> p.ps_shift) : key / p.ps;
       const int page = blk < p.bt_width ? bt[blk - bt_first] : -1;
       ok = page >= 0 && page < p.num_pages;
-      if (ok) off = (((size_t)page * p.cache_Hkv + hk / p.kv_div) * p.ps + (key - blk * p.ps)) * D + ch * 8;
+      if (ok) off = (((size_t)page * p.cache_Hkv + hkc) * p.ps + (key - blk * p.ps)) * D + ch * 8;
     }
     cp_async16(Ks + row * LDS + ch * 8, p.kc + off, ok);
     if (!p.shared_kv) cp_async16(Vs + row * LDS + ch * 8, p.vc + off, ok);
@@ -278,6 +279,7 @@ __global__ void __launch_bounds__(THREADS, (D <= 64 ? 4 : 1)) attention_wide_ker
       bt_first = b_lo;
     }
   }
+  const int stage_elems = (p.shared_kv ? 1 : 2) * BN * LDS;     // keys that are the values too need no second tile
   load_kv_tile(p, bt, bt_first, hk, kt0, lo, hi, KVs, KVs + BN * LDS);
   cp_async_commit();
 
@@ -295,10 +297,10 @@ __global__ void __launch_bounds__(THREADS, (D <= 64 ? 4 : 1)) attention_wide_ker
 
   for (int it = 0; it < n_tiles; ++it) {
     const int kt = kt0 + it * BN;
-    bf16* Ks = KVs + (it & 1) * 2 * BN * LDS;
+    bf16* Ks = KVs + (it & 1) * stage_elems;
     bf16* Vs = p.shared_kv ? Ks : Ks + BN * LDS;
     if (it + 1 < n_tiles) {
-      bf16* Kn = KVs + ((it + 1) & 1) * 2 * BN * LDS;
+      bf16* Kn = KVs + ((it + 1) & 1) * stage_elems;
       load_kv_tile(p, bt, bt_first, hk, kt + BN, lo, hi, Kn, Kn + BN * LDS);
       cp_async_commit();
       cp_async_wait<1>();
@@ -428,7 +430,7 @@ __global__ void __launch_bounds__(THREADS, (D <= 64 ? 4 : 1)) attention_wide_ker
   }
 }
 
-size_t wide_smem_bytes() { return (size_t)(64 + 2 * 2 * BN) * LDS * sizeof(bf16); }
+size_t wide_smem_bytes(bool shared_kv) { return (size_t)(64 + 2 * (shared_kv ? 1 : 2) * BN) * LDS * sizeof(bf16); }
 
 // The deep shape, for requests with at most 16 rows (decoding). grid (splits, Hkv, R), 4 warps. The keys of the
 // block's split are dealt to the warps in sub-tiles of DKW (warp w takes sub-tiles w, w+4, ...); every warp runs
@@ -446,11 +448,12 @@ constexpr int DCOPIES = DKW * CHUNKS / 32;                // 16-byte copies per 
 // Sub-tile of keys [k0, k0 + DKW) of kv head hk -> one stage. Keys outside [lo, hi) become zeros.
 __device__ __forceinline__ void load_kv_subtile(const Params& p, const int* bt, int bt_first, int hk, int k0, int lo, int hi,
                                                 bool same_page, bf16* Ks, bf16* Vs, int lane) {
+  const int hkc = hk / p.kv_div;                 // the cached head this group of query heads reads
   if (same_page) {
     const int blk = p.ps_shift >= 0 ? (k0 >> p.ps_shift) : k0 / p.ps;
     const int page = blk < p.bt_width ? bt[blk - bt_first] : -1;
     const bool page_ok = page >= 0 && page < p.num_pages;
-    const size_t base = (((size_t)(page_ok ? page : 0) * p.cache_Hkv + hk / p.kv_div) * p.ps + (k0 - blk * p.ps)) * D;
+    const size_t base = (((size_t)(page_ok ? page : 0) * p.cache_Hkv + hkc) * p.ps + (k0 - blk * p.ps)) * D;
     const bool inner = page_ok && k0 >= lo && k0 + DKW <= hi;
 #pragma unroll
     for (int i = 0; i < DCOPIES; ++i) {
@@ -468,7 +471,7 @@ __device__ __forceinline__ void load_kv_subtile(const Params& p, const int* bt, 
     const int blk = k0 >> 4;
     const int page_a = blk < p.bt_width ? bt[blk - bt_first] : -1, page_b = blk + 1 < p.bt_width ? bt[blk + 1 - bt_first] : -1;
     const bool ok_a = page_a >= 0 && page_a < p.num_pages, ok_b = page_b >= 0 && page_b < p.num_pages;
-    const size_t base_a = ((size_t)(ok_a ? page_a : 0) * p.cache_Hkv + hk / p.kv_div) * 16 * D, base_b = ((size_t)(ok_b ? page_b : 0) * p.cache_Hkv + hk / p.kv_div) * 16 * D;
+    const size_t base_a = ((size_t)(ok_a ? page_a : 0) * p.cache_Hkv + hkc) * 16 * D, base_b = ((size_t)(ok_b ? page_b : 0) * p.cache_Hkv + hkc) * 16 * D;
     const bool inner = k0 >= lo && k0 + DKW <= hi;
 #pragma unroll
     for (int i = 0; i < DCOPIES; ++i) {
@@ -493,7 +496,7 @@ __device__ __forceinline__ void load_kv_subtile(const Params& p, const int* bt, 
       const int blk = p.ps_shift >= 0 ? (key >> p.ps_shift) : key / p.ps;
       const int page = blk < p.bt_width ? bt[blk - bt_first] : -1;
       ok = page >= 0 && page < p.num_pages;
-      if (ok) off = (((size_t)page * p.cache_Hkv + hk / p.kv_div) * p.ps + (key - blk * p.ps)) * D + ch * 8;
+      if (ok) off = (((size_t)page * p.cache_Hkv + hkc) * p.ps + (key - blk * p.ps)) * D + ch * 8;
     }
     cp_async16(Ks + row * LDS + ch * 8, p.kc + off, ok);
     if (!p.shared_kv) cp_async16(Vs + row * LDS + ch * 8, p.vc + off, ok);
@@ -581,11 +584,12 @@ __global__ void __launch_bounds__(NWARPS * 32) attention_deep_kernel(const Param
   const int k_first = (lo / DKW) * DKW;
   const int n_sub = (hi - k_first + DKW - 1) / DKW;             // sub-tiles of the split
   const int my_n = (n_sub - warp + NWARPS - 1) / NWARPS;        // this warp's share: sub-tiles warp, warp+NWARPS, ...
-  bf16* myKV = KVs + (size_t)warp * DSTAGES * 2 * DKW * LDS;
+  const int stage_elems = (p.shared_kv ? 1 : 2) * DKW * LDS;    // keys that are the values too need no second sub-tile
+  bf16* myKV = KVs + (size_t)warp * DSTAGES * stage_elems;
 #pragma unroll
   for (int s = 0; s < DSTAGES - 1; ++s) {
-    if (s < my_n) load_kv_subtile(p, bt, bt_first, hk, k_first + (warp + NWARPS * s) * DKW, lo, hi, same_page, myKV + s * 2 * DKW * LDS,
-                                  myKV + s * 2 * DKW * LDS + DKW * LDS, lane);
+    if (s < my_n) load_kv_subtile(p, bt, bt_first, hk, k_first + (warp + NWARPS * s) * DKW, lo, hi, same_page, myKV + s * stage_elems,
+                                  myKV + s * stage_elems + DKW * LDS, lane);
     cp_async_commit();
   }
   uint32_t qf[DQ_IN_REGS ? D / 16 : 1][4];
@@ -615,14 +619,14 @@ __global__ void __launch_bounds__(NWARPS * 32) attention_deep_kernel(const Param
     {
       const int nx = it + DSTAGES - 1;
       if (nx < my_n) {
-        bf16* Kn = myKV + (nx % DSTAGES) * 2 * DKW * LDS;
+        bf16* Kn = myKV + (nx % DSTAGES) * stage_elems;
         load_kv_subtile(p, bt, bt_first, hk, k_first + (warp + NWARPS * nx) * DKW, lo, hi, same_page, Kn, Kn + DKW * LDS, lane);
       }
       cp_async_commit();
       cp_async_wait<DSTAGES - 1>();
     }
     __syncwarp();
-    const bf16* Ks = myKV + (it % DSTAGES) * 2 * DKW * LDS;
+    const bf16* Ks = myKV + (it % DSTAGES) * stage_elems;
     const bf16* Vs = p.shared_kv ? Ks : Ks + DKW * LDS;
     const int kbase = k_first + (warp + NWARPS * it) * DKW;
     float s[DNT][4];
@@ -783,8 +787,8 @@ __global__ void __launch_bounds__(NWARPS * 32) attention_deep_kernel(const Param
   if (!last) finish_split(p, r, hk, q0, M, NTHR, reinterpret_cast<float*>(smem_raw));
 }
 
-size_t deep_smem_bytes(int nwarps) {
-  const size_t tiles = (size_t)(16 + nwarps * DSTAGES * 2 * DKW) * LDS * sizeof(bf16);
+size_t deep_smem_bytes(int nwarps, bool shared_kv = false) {
+  const size_t tiles = (size_t)(16 + nwarps * DSTAGES * (shared_kv ? 1 : 2) * DKW) * LDS * sizeof(bf16);
   const size_t merge = (size_t)(nwarps * 16 * D + nwarps * 16 * 2) * sizeof(float);
   return tiles > merge ? tiles : merge;
 }
@@ -792,7 +796,7 @@ size_t deep_smem_bytes(int nwarps) {
 template <bool UPPER, int NWARPS>
 int launch_deep(const Params& p, int n_rows, cudaStream_t stream) {
   auto k = attention_deep_kernel<UPPER, NWARPS>;
-  const size_t smem = deep_smem_bytes(NWARPS);
+  const size_t smem = deep_smem_bytes(NWARPS, p.shared_kv != 0);
   if (smem > 48 * 1024) cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   SB_PDL_CHECK(launch_pdl(k, dim3(p.num_splits, p.Hkv, n_rows), dim3(NWARPS * 32), smem, stream, p));
   return 0;
@@ -848,7 +852,7 @@ SB_EXPORT int sb_attention_mma_opts(const void* qkv, int q_stride, const void* k
   p.wide_rows = wide_rows; p.heads_in_x = 0;
   if (which & 1) {
     auto k = attention_wide_kernel;
-    const size_t smem = wide_smem_bytes();
+    const size_t smem = wide_smem_bytes(p.shared_kv != 0);
     if (smem > 48 * 1024) cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     const long long tiles = ((long long)max_q * p.G + 63) / 64;
     if (tiles > 2147483647LL) return SB_ERR_LIMIT;
@@ -868,7 +872,8 @@ SB_EXPORT int sb_attention_mma_opts(const void* qkv, int q_stride, const void* k
     }
     // bit 2 of ``which``: some request has more than 8 rows (the caller knows the largest token count).
     // Few blocks (at most one per SM): 8 warps each, so that an SM still has warps to switch between.
-    const bool roomy = (long long)n_rows * Hkv * num_splits <= sm_count() && deep_smem_bytes(8) <= 227 * 1024;
+    const bool shared = p.shared_kv != 0;
+    const bool roomy = (long long)n_rows * Hkv * num_splits <= sm_count() && deep_smem_bytes(8, shared) <= 227 * 1024;
     // Otherwise the block shape follows from what fits the SMs at once (two four-warp blocks an SM at head_dim 64, five
     // two-warp blocks, ten one-warp blocks) and from how long the sequences can be (``longest``, 0 if the caller does
     // not say). A block's fixed part (table, queries, first loads, merge, store) is 4-5 us: it should overlap with
@@ -883,7 +888,7 @@ SB_EXPORT int sb_attention_mma_opts(const void* qkv, int q_stride, const void* k
     //    296 + 24: 35.2 against 42.8), unless their own last round would be thin and one-warp blocks fit at once
     //    (100 requests x 300 tokens: 17.1 us with one warp, 20.2 with two).
     const long long pairs = (long long)n_rows * Hkv, blocks = pairs * num_splits;
-    auto at_once = [&](int nw) { return (long long)sm_count() * (long long)std::max<size_t>(1, (227 * 1024) / (deep_smem_bytes(nw) + 2048)); };
+    auto at_once = [&](int nw) { return (long long)sm_count() * (long long)std::max<size_t>(1, (227 * 1024) / (deep_smem_bytes(nw, shared) + 2048)); };
     const long long cap4 = at_once(4), cap2 = at_once(2), cap1 = at_once(1);
     auto thin_last_round = [&](long long cap) {          // the last round of blocks would be under 70 % full
       const long long rounds = (blocks + cap - 1) / cap;

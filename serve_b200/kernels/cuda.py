@@ -518,6 +518,7 @@ class CudaKernels:
     MAX_SPLITS = 32
     # query heads per group when all heads share one cached row per token (SERVE_B200_LATENT_GROUP for measurements)
     LATENT_GROUP = int(os.environ.get("SERVE_B200_LATENT_GROUP", "8"))
+    LATENT_GROUP_DECODE = int(os.environ.get("SERVE_B200_LATENT_GROUP_DECODE", "4"))
 
     def split_plan(self, rows: int, kv_heads: int, max_kv: int) -> int:
         """Number of key splits of the deep shape for a batch; a function of sizes only, never of data.
@@ -532,9 +533,13 @@ class CudaKernels:
         # few rows, which the deep shape spreads over the SMs with its key splits; as one pair of 32 rows it would be a single
         # block of the wide shape walking all keys alone. For prompt portions the grouping changes neither work nor traffic.
         kv_div = 1
-        if k_cache is v_cache and kv_heads * self.LATENT_GROUP < heads and heads % (kv_heads * self.LATENT_GROUP) == 0:
-            kv_div = heads // (kv_heads * self.LATENT_GROUP)
-            kv_heads = kv_heads * kv_div
+        if k_cache is v_cache:
+            # (a step of single tokens takes smaller groups: measured at batch 8 after 2,048 tokens, groups of 4 against 8 give
+            # 29 against 38 us a launch with 8 heads and 31 against 39 us with 16)
+            per_group = self.LATENT_GROUP_DECODE if shape.max_q == 1 else self.LATENT_GROUP
+            if kv_heads * per_group < heads and heads % (kv_heads * per_group) == 0:
+                kv_div = heads // (kv_heads * per_group)
+                kv_heads = kv_heads * kv_div
         group = heads // kv_heads
         min_q = getattr(shape, "min_q", 1)
         which = 0

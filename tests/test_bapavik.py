@@ -622,11 +622,11 @@ def test_latent_attention_with_many_heads_in_groups(backend, heads, group):
     want = P.latent_attention(x.double(), {k: v.double() for k, v in w.items()}, "t.", m, 1e-5).float()
     spec = _mixer_spec("latent_attention", m, width, 1e-5, "t.")
     rt, _ = runtime_for(backend)
-    before = rt.kernels.LATENT_GROUP
-    rt.kernels.LATENT_GROUP = group
+    before = (rt.kernels.LATENT_GROUP, rt.kernels.LATENT_GROUP_DECODE)
+    rt.kernels.LATENT_GROUP = rt.kernels.LATENT_GROUP_DECODE = group
     try:
         for cuts in ([730], [700, 3, 2] + [1] * 25):
             got = _run_part(backend, "mixer", spec, w, x, cuts, page=16)
             torch.testing.assert_close(got, want, atol=_tol(backend, want), rtol=0)
     finally:
-        rt.kernels.LATENT_GROUP = before
+        rt.kernels.LATENT_GROUP, rt.kernels.LATENT_GROUP_DECODE = before
