@@ -154,16 +154,18 @@ __global__ void __launch_bounds__(256) normed_qk_cache_write_kernel(
 
 // ------------------------------------------------------------------------------------------------ latent attention
 // proj [T, stride]: columns [0, n_q) are H query heads of (dim + rd) each, [n_q, n_q + rank) the latent vector, then rd
-// of the shared key part. Writes, per token: the cache row [c * inv_rms * weight | rotated key part | zeros] of D
-// elements (one key/value head), and for every head columns [rank, D) of q_lat [T, H * D]: the rotated query part,
-// then zeros (columns [0, rank) are the product of the plain query part with the keys' read-out matrix, made elsewhere).
+// of the shared key part. Writes, per token: the row [c * inv_rms * weight | rotated key part | zeros] of D elements into
+// the cache (one key/value head) and, if asked, into row_out [T, row_stride] (its first rank + rd columns); and for every
+// head columns [q_off, D) of q_lat (rows q_stride apart, heads D apart): the rotated query part, then zeros (columns
+// [0, q_off) are made elsewhere: the product of the plain query part with the keys' read-out matrix when q_off = rank,
+// the plain query part itself when q_off = dim).
 // Rotation: pairs (2 i, 2 i + 1), i < rot_dims / 2, angle = float(position) * inv_freq[i]; the rest passes unchanged.
 template <typename T>
 __global__ void __launch_bounds__(128) latent_prepare_kernel(
     const T* __restrict__ proj, int stride, int n_q, const int* __restrict__ positions, const int* __restrict__ token_row,
     const float* __restrict__ c_weight, float eps, const float* __restrict__ inv_freq, int rot_dims, int H, int dim, int rd, int rank,
-    int D, T* __restrict__ q_lat, T* __restrict__ kc, const int* __restrict__ block_table, int bt_width, int ps, int num_pages,
-    int write_cache, int* __restrict__ errors) {
+    int D, T* __restrict__ q_lat, int q_stride, int q_off, T* __restrict__ row_out, int row_stride, T* __restrict__ kc,
+    const int* __restrict__ block_table, int bt_width, int ps, int num_pages, int write_cache, int* __restrict__ errors) {
   __shared__ float red[32];
   extern __shared__ float cs[];            // [rot_dims / 2][2]: cosine and sine of the token's angles
   const int t = blockIdx.x;
@@ -187,11 +189,17 @@ __global__ void __launch_bounds__(128) latent_prepare_kernel(
     const float u = to_float(src[2 * i]), v = to_float(src[2 * i + 1]);
     return (j & 1) ? v * cs[2 * i] + u * cs[2 * i + 1] : u * cs[2 * i] - v * cs[2 * i + 1];
   };
-  const int tail = D - rank;               // columns of a head after the latent part
+  const int tail = D - q_off;              // columns of a head from the rotated part on
   for (int w = threadIdx.x; w < H * tail; w += blockDim.x) {
     const int h = w / tail, j = w - h * tail;
     const float v = j < rd ? rotated(row + (size_t)h * (dim + rd) + dim, j) : 0.f;
-    q_lat[((size_t)t * H + h) * D + rank + j] = from_float<T>(v);
+    q_lat[(size_t)t * q_stride + (size_t)h * D + q_off + j] = from_float<T>(v);
+  }
+  if (row_out != nullptr) {
+    for (int i = threadIdx.x; i < rank + rd; i += blockDim.x) {
+      const float v = i < rank ? to_float(row[n_q + i]) * inv * c_weight[i] : rotated(row + n_q + rank, i - rank);
+      row_out[(size_t)t * row_stride + i] = from_float<T>(v);
+    }
   }
   if (!write_cache) return;
   const int blk = pos / ps;
@@ -200,8 +208,9 @@ __global__ void __launch_bounds__(128) latent_prepare_kernel(
     if (threadIdx.x == 0) atomicAdd(errors, 1);
     return;
   }
-  T* dst = kc + ((size_t)page * ps + (pos - blk * ps)) * D;
-  for (int i = threadIdx.x; i < D; i += blockDim.x) {
+  const int Dc = rank + rd <= D ? D : 0;   // (a cache row is written only where it fits: the caller checks)
+  T* dst = kc + ((size_t)page * ps + (pos - blk * ps)) * Dc;
+  for (int i = threadIdx.x; i < Dc; i += blockDim.x) {
     float v = 0.f;
     if (i < rank) v = to_float(row[n_q + i]) * inv * c_weight[i];
     else if (i < rank + rd) v = rotated(row + n_q + rank, i - rank);
@@ -305,23 +314,27 @@ SB_EXPORT int sb_normed_qk_cache_write(void* proj, int stride, const int* positi
 
 SB_EXPORT int sb_latent_prepare(const void* proj, int stride, int n_q, const int* positions, const int* token_row, const float* c_weight,
                                 float eps, const float* inv_freq, int rot_dims, int H, int dim, int rd, int rank, int D, void* q_lat,
-                                void* kc, const int* block_table, int bt_width, int ps, int num_pages, int write_cache, int* errors,
-                                int n_tokens, int dtype, cudaStream_t stream) {
+                                int q_stride, int q_off, void* row_out, int row_stride, void* kc, const int* block_table, int bt_width,
+                                int ps, int num_pages, int write_cache, int* errors, int n_tokens, int dtype, cudaStream_t stream) {
   if (n_tokens <= 0) return 0;
-  if (H <= 0 || dim <= 0 || rd <= 0 || rank <= 0 || rot_dims < 0 || (rot_dims & 1) || rot_dims > rd || D < rank + rd ||
-      n_q != H * (dim + rd) || stride < n_q + rank + rd)
+  if (H <= 0 || dim <= 0 || rd <= 0 || rank <= 0 || rot_dims < 0 || (rot_dims & 1) || rot_dims > rd || q_off < 0 || D < q_off + rd ||
+      q_stride < H * D || n_q != H * (dim + rd) || stride < n_q + rank + rd)
     return SB_ERR_SHAPE;
+  if (write_cache && D < rank + rd) return SB_ERR_SHAPE;
+  if (row_out != nullptr && row_stride < rank + rd) return SB_ERR_SHAPE;
   if (write_cache && (ps <= 0 || bt_width <= 0 || !kc || !errors)) return SB_ERR_SHAPE;
   const size_t smem = (size_t)(rot_dims > 0 ? rot_dims : 2) * sizeof(float);
   if (smem > 48 * 1024) return SB_ERR_LIMIT;
   if (dtype == SB_DTYPE_F32)
     latent_prepare_kernel<float><<<n_tokens, 128, smem, stream>>>((const float*)proj, stride, n_q, positions, token_row, c_weight, eps,
-                                                                   inv_freq, rot_dims, H, dim, rd, rank, D, (float*)q_lat, (float*)kc,
-                                                                   block_table, bt_width, ps, num_pages, write_cache, errors);
+                                                                   inv_freq, rot_dims, H, dim, rd, rank, D, (float*)q_lat, q_stride, q_off,
+                                                                   (float*)row_out, row_stride, (float*)kc, block_table, bt_width, ps,
+                                                                   num_pages, write_cache, errors);
   else if (dtype == SB_DTYPE_BF16)
     latent_prepare_kernel<__nv_bfloat16><<<n_tokens, 128, smem, stream>>>(
         (const __nv_bfloat16*)proj, stride, n_q, positions, token_row, c_weight, eps, inv_freq, rot_dims, H, dim, rd, rank, D,
-        (__nv_bfloat16*)q_lat, (__nv_bfloat16*)kc, block_table, bt_width, ps, num_pages, write_cache, errors);
+        (__nv_bfloat16*)q_lat, q_stride, q_off, (__nv_bfloat16*)row_out, row_stride, (__nv_bfloat16*)kc, block_table, bt_width, ps, num_pages,
+        write_cache, errors);
   else
     return SB_ERR_DTYPE;
   SB_LAUNCH_CHECK();

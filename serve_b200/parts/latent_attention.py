@@ -13,6 +13,10 @@ once per cached key: q_plain . (U_n c) = (U_n^T q_plain) . c, so the query becom
 attention is one over a single shared key/value head whose keys and values are the same cached rows; the attention's
 output per head, sum_j p_j c_j, then goes through V_n and the output projection. Both per-head products are batched
 library products. The cache's value tensor is its key tensor (``CacheNeed.shared_kv``).
+
+The attention kernels' rows end at 256 numbers. A model whose kv_rank + rot_dim is larger runs the other way round: every
+head's key [U_n c | rotated part] and value V_n c are read out when the token arrives and cached in ordinary pages, one
+key/value head per query head (``per_head``; more cache, the same results).
 """
 from __future__ import annotations
 
@@ -25,7 +29,10 @@ from .base import CacheNeed, Mixer, TensorDecl, register_part
 
 @register_part("mixer", "latent_attention")
 class LatentAttention(Mixer):
-    """params: hidden, heads, dim, rot_dim, vdim, kv_rank, scale, rot_base, rot_dims (default rot_dim), eps, window (None), names."""
+    """params: hidden, heads, dim, rot_dim, vdim, kv_rank, scale, rot_base, rot_dims (default rot_dim), eps, window (None), names,
+    per_head (default: only when kv_rank + rot_dim exceeds the attention kernels' widest row)."""
+
+    MAX_ROW = 256        # the widest head the attention kernels take
 
     def __init__(self, spec, runtime):
         super().__init__(spec, runtime)
@@ -42,8 +49,14 @@ class LatentAttention(Mixer):
         self.names = dict(p.get("names", {}))
         self.row = self.rank + self.rot_dim                       # what a token leaves in the cache
         self.head_dim = 16 * -(-self.row // 16)
-        self.mixed_size = self.heads * self.vdim
-        runtime.kernels.check_attention_shape(self.heads, 1, self.head_dim)
+        self.per_head = bool(p.get("per_head", self.head_dim > self.MAX_ROW))
+        if self.per_head:
+            self.head_dim = 16 * -(-max(self.dim + self.rot_dim, self.vdim) // 16)
+            self.mixed_size = self.heads * self.head_dim
+            runtime.kernels.check_attention_shape(self.heads, self.heads, self.head_dim)
+        else:
+            self.mixed_size = self.heads * self.vdim
+            runtime.kernels.check_attention_shape(self.heads, 1, self.head_dim)
 
     def _name(self, key):
         return self.prefix + self.names.get(key, key)
@@ -71,11 +84,20 @@ class LatentAttention(Mixer):
         # U_n^T as the [N, K] operand of out = a @ w^T: [heads, kv_rank, dim]
         self.w_uk_t = tensors[self._name("uk")].view(self.heads, self.dim, self.rank).transpose(1, 2).contiguous()
         self.w_uv = tensors[self._name("uv")].view(self.heads, self.vdim, self.rank).contiguous()
-        self.w_o = tensors[self._name("o")].contiguous()
+        w_o = tensors[self._name("o")]
+        if self.per_head:
+            self.w_uk = tensors[self._name("uk")].view(self.heads, self.dim, self.rank).contiguous()
+            if self.vdim != self.head_dim:
+                padded = w_o.new_zeros((self.hidden, self.heads, self.head_dim))
+                padded[:, :, : self.vdim] = w_o.view(self.hidden, self.heads, self.vdim)
+                w_o = padded.view(self.hidden, self.heads * self.head_dim)
+        self.w_o = w_o.contiguous()
         i = torch.arange(self.rot_dims // 2, dtype=torch.float64)
         self.inv_freq = (self.rot_base ** (-2.0 * i / self.rot_dims)).to(torch.float32).to(self.w_o.device)
 
     def cache_need(self):
+        if self.per_head:
+            return CacheNeed(kv_heads=self.heads, head_dim=self.head_dim, window=self.window)
         return CacheNeed(kv_heads=1, head_dim=self.head_dim, window=self.window, shared_kv=True)
 
     def output_weight(self):
@@ -89,6 +111,8 @@ class LatentAttention(Mixer):
         proj = self.rt.empty_act((t, self.n_in))
         k.linear(h, self.w_in, proj)
         table = ctx.block_tables[cache.group]
+        if self.per_head:
+            return self._mix_per_head(proj, ctx, cache, table, out)
         q_lat = self.rt.empty_act((t, self.heads * d))             # per head [U^T q_plain | q_rot | zeros]
         k.latent_prepare(proj, self.n_q, ctx.positions, ctx.token_row, self.c_norm, self.eps, self.inv_freq, self.rot_dims, self.heads,
                          self.dim, self.rot_dim, self.rank, d, q_lat, cache.k, table, cache.page_size, cache.writes)
@@ -98,6 +122,26 @@ class LatentAttention(Mixer):
         k.attention(q_lat, cache.k, cache.v, table, ctx.cu_q, ctx.kv_len, ctx.token_row, ctx.positions, self.heads, 1, d,
                     cache.page_size, self.scale, self.window or 0, o_lat, ctx.shape)
         k.linear_batched(o_lat.view(t, self.heads, d)[:, :, : self.rank], self.w_uv, out.view(t, self.heads, self.vdim))
+
+    def _mix_per_head(self, proj, ctx, cache, table, out):
+        """Keys and values read out per head when the token arrives: qkv [T, 3 H, D] = queries [q_plain | q_rot], keys
+        [U_n c | k_rot], values V_n c (zeros after each), cached like any attention's."""
+        k = self.rt.kernels
+        t, d, hh = proj.shape[0], self.head_dim, self.heads
+        qkv = torch.zeros((t, 3 * hh * d), dtype=proj.dtype, device=proj.device)
+        row = self.rt.empty_act((t, 8 * -(-self.row // 8)))
+        k.latent_prepare(proj, self.n_q, ctx.positions, ctx.token_row, self.c_norm, self.eps, self.inv_freq, self.rot_dims, hh, self.dim,
+                         self.rot_dim, self.rank, d, qkv, None, table, cache.page_size, False, q_off=self.dim, row_out=row)
+        q3 = qkv.view(t, 3 * hh, d)
+        q3[:, :hh, : self.dim].copy_(proj[:, : self.n_q].view(t, hh, self.dim + self.rot_dim)[:, :, : self.dim])
+        c = row[:, None, : self.rank].expand(t, hh, self.rank)
+        k.linear_batched(c, self.w_uk, q3[:, hh: 2 * hh, : self.dim])
+        q3[:, hh: 2 * hh, self.dim: self.dim + self.rot_dim].copy_(row[:, None, self.rank: self.row].expand(t, hh, self.rot_dim))
+        k.linear_batched(c, self.w_uv, q3[:, 2 * hh:, : self.vdim])
+        k.normed_qk_cache_write(qkv, ctx.positions, ctx.token_row, hh, hh, d, d, None, None, 0.0, 0.0, 1, cache.k, cache.v, table,
+                                cache.page_size, cache.writes)
+        k.attention(qkv, cache.k, cache.v, table, ctx.cu_q, ctx.kv_len, ctx.token_row, ctx.positions, hh, hh, d, cache.page_size,
+                    self.scale, self.window or 0, out, ctx.shape)
 
     def forward(self, h, ctx, cache):
         mixed = self.rt.empty_act((h.shape[0], self.mixed_size))

@@ -158,7 +158,7 @@ class EmuKernels:
             self._write_pages(v_cache, x[:, heads + kv_heads:], positions, token_row, block_table, page_size)
 
     def latent_prepare(self, proj, n_q, positions, token_row, c_weight, eps, inv_freq, rot_dims, heads, dim, rot_dim, rank, head_dim,
-                       q_lat, k_cache, block_table, page_size, write_cache):
+                       q_lat, k_cache, block_table, page_size, write_cache, q_off=None, row_out=None):
         t, m = proj.shape[0], self.math
         ang = positions.to(torch.float32)[:, None] * inv_freq.to(torch.float32)[None, :]
         cos, sin = ang.cos().to(m), ang.sin().to(m)
@@ -170,12 +170,16 @@ class EmuKernels:
             return torch.cat([torch.stack([a * c - b * s, b * c + a * s], -1).flatten(-2), v[..., rot_dims:]], -1)
 
         q = proj[:, :n_q].view(t, heads, dim + rot_dim).to(m)
-        ql = q_lat.view(t, heads, head_dim)
-        ql[:, :, rank: rank + rot_dim] = rotate(q[..., dim:]).to(q_lat.dtype)
-        ql[:, :, rank + rot_dim:] = 0
+        q_off = rank if q_off is None else q_off
+        ql = q_lat[:, : heads * head_dim].view(t, heads, head_dim)
+        ql[:, :, q_off: q_off + rot_dim] = rotate(q[..., dim:]).to(q_lat.dtype)
+        ql[:, :, q_off + rot_dim:] = 0
         down = proj[:, n_q: n_q + rank + rot_dim].to(m)
         c = down[:, :rank]
         c = c * torch.rsqrt(c.pow(2).mean(-1, keepdim=True) + eps) * c_weight.to(m)
+        if row_out is not None:
+            row_out[:, :rank] = c.to(row_out.dtype)
+            row_out[:, rank: rank + rot_dim] = rotate(down[:, rank:]).to(row_out.dtype)
         if write_cache:
             row = torch.zeros((t, 1, head_dim), dtype=m, device=proj.device)
             row[:, 0, :rank] = c

@@ -630,3 +630,31 @@ def test_latent_attention_with_many_heads_in_groups(backend, heads, group):
             torch.testing.assert_close(got, want, atol=_tol(backend, want), rtol=0)
     finally:
         rt.kernels.LATENT_GROUP, rt.kernels.LATENT_GROUP_DECODE = before
+
+
+@pytest.mark.parametrize("backend", BACKENDS)
+@pytest.mark.parametrize("rank,rot", [(272, 16), (40, 8)])
+def test_latent_attention_that_caches_keys_and_values_per_head(backend, rank, rot):
+    """A latent row wider than the attention kernels' widest head (272 + 16 > 256) is read out per head when the token
+    arrives and cached in ordinary pages; asked for by name the same path runs at any size. Same results."""
+    from serve_b200.models.bapavik import _mixer_spec
+
+    m = {"heads": 3, "dim": 24, "rot_dim": rot, "vdim": 40, "kv_rank": rank, "scale": 0.2, "rot": {"base": 5000.0, "dims": rot}}
+    width = 96
+    g = torch.Generator().manual_seed(rank)
+    rnd = lambda *shape: (torch.randn(*shape, generator=g) * 1.5 / shape[-1] ** 0.5).bfloat16().float()
+    w = {"t.q": rnd(3 * (24 + rot), width), "t.dkv": rnd(rank + rot, width), "t.dkv.norm": (1 + 0.2 * torch.randn(rank, generator=g)).bfloat16().float(),
+         "t.uk": rnd(3 * 24, rank), "t.uv": rnd(3 * 40, rank), "t.o": rnd(width, 3 * 40)}
+    x = torch.randn(75, width, generator=g).bfloat16().float()
+    want = P.latent_attention(x.double(), {k: v.double() for k, v in w.items()}, "t.", m, 1e-5).float()
+    spec = _mixer_spec("latent_attention", m, width, 1e-5, "t.")
+    spec.params["per_head"] = True
+    rt, _ = runtime_for(backend)
+    part = build_part("mixer", spec, rt)
+    assert part.per_head and part.cache_need().kv_heads == 3 and not part.cache_need().shared_kv
+    if rank + rot > 256:
+        auto = build_part("mixer", _mixer_spec("latent_attention", m, width, 1e-5, "t."), rt)
+        assert auto.per_head
+    for cuts in ([75], [40, 2, 1, 1, 30, 1]):
+        got = _run_part(backend, "mixer", spec, w, x, cuts, page=16)
+        torch.testing.assert_close(got, want, atol=_tol(backend, want), rtol=0)
