@@ -150,7 +150,20 @@ struct TcParams {
   int* error;
   const int* rows;      // requests this launch covers (blockIdx.z indexes it); nullptr: all, in order
   int heads_in_x;       // grid (kv heads, row tiles, requests) rather than (row tiles, kv heads, requests)
+  // A cap c on the scaled scores (s -> c tanh(s / c)): softcap_in = scale / c is what a raw product is multiplied by inside
+  // the tanh, cap_over_scale = c / scale what the tanh is multiplied by, so that the capped value is again a raw product
+  // that the code below scales; both 0 without a cap. sinks: one float per query head, or null: exp(sink) joins the
+  // softmax's denominator once per row (no key, no value).
+  float softcap_in, cap_over_scale;
+  const float* sinks;
 };
+
+// tanh on the special-function unit, as the exponentials (relative error about 2^-11)
+__device__ __forceinline__ float tanh_fast(float x) {
+  float y;
+  asm("tanh.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
 
 __global__ void __launch_bounds__(THREADS, CTAS_PER_SM) attention_tc_kernel(const __grid_constant__ CUtensorMap map_q,
                                                                const __grid_constant__ CUtensorMap map_k,
@@ -352,6 +365,10 @@ __global__ void __launch_bounds__(THREADS, CTAS_PER_SM) attention_tc_kernel(cons
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&s_empty[b]);           // the scores are in registers: the buffer may be reused
+      if (p.cap_over_scale > 0.f) {                      // the cap comes before the mask: tanh(-inf) would be finite
+#pragma unroll
+        for (int i = 0; i < BN; ++i) sv[i] = p.cap_over_scale * tanh_fast(sv[i] * p.softcap_in);
+      }
       if (masked) {
 #pragma unroll
         for (int i = 0; i < BN; ++i) sv[i] = (kt + i <= pos) ? sv[i] : -INFINITY;
@@ -426,6 +443,12 @@ __global__ void __launch_bounds__(THREADS, CTAS_PER_SM) attention_tc_kernel(cons
       if (!mbar_wait(&p_empty[pb], ((n_tiles - 1) >> 1) & 1)) failed = true;
       tc_fence_after();
       if (!failed) {
+        if (p.sinks != nullptr && row_ok) {
+          // the sums were taken against m_ref; so is the sink (a sink far above every score makes the sum infinite and
+          // the row zero, which is its limit)
+          const float sk = p.sinks[head] * LOG2E;
+          l_run += (m_ref == -INFINITY) ? 1.f : exp2f(sk - m_ref);
+        }
         const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
         float ov[D];
 #pragma unroll
@@ -487,9 +510,11 @@ SB_EXPORT int sb_attention_tc_supports(int H, int Hkv, int ps, int window, int q
 // The wide shape of sb_attention_mma (requests with more than 16 rows) on tcgen05; arguments as there.
 // n_tokens: rows of qkv; num_pages: pages of kc / vc. rows (may be null): the n_rows requests to cover, so that a
 // step of hundreds of decoding requests and a few prompt portions launches blocks for the portions only.
-SB_EXPORT int sb_attention_tc(const void* qkv, int q_stride, int n_tokens, const void* kc, const void* vc, const int* block_table,
-                              int bt_width, const int* cu_q, const int* kv_len, int H, int Hkv, int ps, int num_pages, float scale,
-                              void* out, int n_rows, int max_q, const int* rows, int* error, cudaStream_t stream) {
+// softcap (0: none) and sinks (float [H] or null): see TcParams.
+SB_EXPORT int sb_attention_tc_opts(const void* qkv, int q_stride, int n_tokens, const void* kc, const void* vc, const int* block_table,
+                                   int bt_width, const int* cu_q, const int* kv_len, int H, int Hkv, int ps, int num_pages, float scale,
+                                   void* out, int n_rows, int max_q, const int* rows, int* error, float softcap, const float* sinks,
+                                   cudaStream_t stream) {
   if (n_rows <= 0 || max_q <= 0) return 0;
   if (!sb_attention_tc_supports(H, Hkv, ps, 0, q_stride)) return SB_ERR_SHAPE;
   if (Hkv > 65535 || n_rows > 65535) return SB_ERR_LIMIT;
@@ -515,6 +540,7 @@ SB_EXPORT int sb_attention_tc(const void* qkv, int q_stride, int n_tokens, const
   TcParams p;
   p.block_table = block_table; p.bt_width = bt_width; p.cu_q = cu_q; p.kv_len = kv_len;
   p.H = H; p.Hkv = Hkv; p.G = G; p.ps = ps; p.scale_log2 = scale * LOG2E; p.out = (bf16*)out; p.error = error; p.rows = rows;
+  p.softcap_in = softcap > 0.f ? scale / softcap : 0.f; p.cap_over_scale = softcap > 0.f ? softcap / scale : 0.f; p.sinks = sinks;
   const int tok_per_tile = BM / G;
   const int m_tiles = (max_q + tok_per_tile - 1) / tok_per_tile;
   auto k = attention_tc_kernel;
@@ -523,6 +549,13 @@ SB_EXPORT int sb_attention_tc(const void* qkv, int q_stride, int n_tokens, const
   const dim3 grid = p.heads_in_x ? dim3(Hkv, m_tiles, n_rows) : dim3(m_tiles, Hkv, n_rows);
   SB_PDL_CHECK(launch_pdl(k, grid, dim3(THREADS), (size_t)SMEM_BYTES, stream, map_q, map_k, map_v, p));
   return 0;
+}
+
+SB_EXPORT int sb_attention_tc(const void* qkv, int q_stride, int n_tokens, const void* kc, const void* vc, const int* block_table,
+                              int bt_width, const int* cu_q, const int* kv_len, int H, int Hkv, int ps, int num_pages, float scale,
+                              void* out, int n_rows, int max_q, const int* rows, int* error, cudaStream_t stream) {
+  return sb_attention_tc_opts(qkv, q_stride, n_tokens, kc, vc, block_table, bt_width, cu_q, kv_len, H, Hkv, ps, num_pages, scale, out,
+                              n_rows, max_q, rows, error, 0.f, nullptr, stream);
 }
 
 #else

@@ -488,8 +488,8 @@ class CudaKernels:
                   page_size, scale, window, out, shape, slopes=None, chunk: int = 0, softcap: float = 0.0, sinks=None) -> None:
         """``slopes`` (float [heads]): slope_h * distance is taken off every score; ``chunk`` > 0: a query sees only the keys of
         its own block of ``chunk`` positions; ``softcap`` c > 0: a scaled score s becomes c * tanh(s / c); ``sinks`` (float
-        [heads]): exp(sink_h) joins the softmax's denominator. In bfloat16 all run on the mma.sync kernels (the tensor-memory
-        kernel takes none of them), in float32 on the plain-arithmetic kernel."""
+        [heads]): exp(sink_h) joins the softmax's denominator. In bfloat16 all run on the mma.sync kernels; cap and sink
+        also on the tensor-memory kernel (prompt portions at head sizes 64 and 128); in float32 on the plain-arithmetic kernel."""
         lib = self._attention_lib(head_dim)
         softcap = float(softcap or 0.0)
         opts = slopes is not None or chunk or softcap > 0.0 or sinks is not None
@@ -570,14 +570,14 @@ class CudaKernels:
                 scratch = self._scratch_buffer(lib, shape.rows, kv_heads, num_splits)
                 tickets = self._ticket_buffer(shape.rows * kv_heads)
         by_distance = slopes is not None or chunk > 0 or softcap > 0.0 or sinks is not None
-        if (which & 1) and not by_distance and kv_div == 1 and self.use_tcgen05_attention and self._tc_attention_takes(lib, heads, kv_heads, head_dim, page_size, window, qkv.shape[1]):
+        if (which & 1) and slopes is None and not chunk and kv_div == 1 and self.use_tcgen05_attention and self._tc_attention_takes(lib, heads, kv_heads, head_dim, page_size, window, qkv.shape[1]):
             # prompt portions on the tensor-memory path; what is left (decoding rows) goes to the deep shape below
             self.launches += 1
-            _check(lib.sb_attention_tc(
+            _check(lib.sb_attention_tc_opts(
                 _p(qkv), qkv.shape[1], qkv.shape[0], _p(k_cache), _p(v_cache), _p(block_table), block_table.shape[1], _p(cu_q),
                 _p(kv_len), heads, kv_heads, page_size, k_cache.shape[0], ctypes.c_float(scale), _p(out),
-                n_wide if wide_rows is not None else shape.rows, shape.max_q, _p(wide_rows), self._wait_flag(), self._s()),
-                "tcgen05 attention")
+                n_wide if wide_rows is not None else shape.rows, shape.max_q, _p(wide_rows), self._wait_flag(),
+                ctypes.c_float(softcap), _p(sinks), self._s()), "tcgen05 attention")
             which &= ~1
             if not which:
                 return

@@ -658,3 +658,26 @@ def test_latent_attention_that_caches_keys_and_values_per_head(backend, rank, ro
     for cuts in ([75], [40, 2, 1, 1, 30, 1]):
         got = _run_part(backend, "mixer", spec, w, x, cuts, page=16)
         torch.testing.assert_close(got, want, atol=_tol(backend, want), rtol=0)
+
+
+@pytest.mark.parametrize("backend", BACKENDS[1:])
+@pytest.mark.parametrize("dim,vdim,kv", [(128, 128, 2), (64, 64, 8), (128, 48, 1), (40, 64, 4)])
+@pytest.mark.parametrize("cap,sink", [(50.0, 0.5), (2.0, -3.0), (None, 6.0), (6.0, 60.0)])
+def test_cap_and_sink_at_head_sizes_of_64_and_128(backend, dim, vdim, kv, cap, sink):
+    """Heads of 64 and 128 (also padded to them) send the prompt portions of the bfloat16 path to the tensor-memory kernel and the
+    decoded tokens to the split-key kernel: a low cap, no cap, sinks below, among and far above the scores, over 700 tokens."""
+    from serve_b200.models.bapavik import _mixer_spec
+
+    m = {"heads": 8, "kv_heads": kv, "dim": dim, "vdim": vdim, "scale": dim ** -0.5, "softcap": cap, "q_temp": {"coef": 0.4, "every": 100}}
+    width = 256
+    g = torch.Generator().manual_seed(dim + vdim)
+    rnd = lambda *shape: (torch.randn(*shape, generator=g) * 1.5 / shape[-1] ** 0.5).bfloat16().float()
+    w = {"t.q": rnd(8 * dim, width), "t.k": rnd(kv * dim, width), "t.v": rnd(kv * vdim, width), "t.o": rnd(width, 8 * vdim),
+         "t.q.norm": (2.0 + 0.3 * torch.randn(8 * dim, generator=g)).bfloat16().float(), "t.k.norm": (1.0 + 0.2 * torch.randn(kv * dim, generator=g)).bfloat16().float(),
+         "t.sink": torch.full((8,), sink) + torch.arange(8) * 0.25}
+    x = torch.randn(700, width, generator=g).bfloat16().float()
+    want = P.sink_attention(x.double(), {k: v.double() for k, v in w.items()}, "t.", dict(m, softcap=cap or 1e9), 1e-5).float()
+    spec = _mixer_spec("attention", m, width, 1e-5, "t.")
+    for cuts in ([700], [300, 390, 2, 3] + [1] * 5):
+        got = _run_part(backend, "mixer", spec, w, x, cuts, page=64, pages=32)
+        torch.testing.assert_close(got, want, atol=max(_tol(backend, want), 1e-6), rtol=0)
