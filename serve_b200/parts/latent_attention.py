@@ -21,6 +21,7 @@ key/value head per query head (``per_head``; more cache, the same results).
 from __future__ import annotations
 
 import math
+import os
 
 import torch
 
@@ -49,7 +50,8 @@ class LatentAttention(Mixer):
         self.names = dict(p.get("names", {}))
         self.row = self.rank + self.rot_dim                       # what a token leaves in the cache
         self.head_dim = 16 * -(-self.row // 16)
-        self.per_head = bool(p.get("per_head", self.head_dim > self.MAX_ROW))
+        # (SERVE_B200_LATENT_PER_HEAD=1: measurements of the other form at any size)
+        self.per_head = bool(p.get("per_head", self.head_dim > self.MAX_ROW or os.environ.get("SERVE_B200_LATENT_PER_HEAD") == "1"))
         if self.per_head:
             self.head_dim = 16 * -(-max(self.dim + self.rot_dim, self.vdim) // 16)
             self.mixed_size = self.heads * self.head_dim
