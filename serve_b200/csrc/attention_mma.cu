@@ -73,7 +73,8 @@ struct Params {
   float scale_log2; int window;
   const float* slopes;   // one per query head, or null: slope * (position - key) is taken off a score (in the score's own units)
   int chunk;             // > 0: a query sees only the keys from floor(position / chunk) * chunk on
-  float softcap_log2;    // > 0: a scaled score s becomes c * tanh(s / c), c the cap (kept here times log2 e), before any bias
+  float cap_over_scale;  // > 0: a scaled score s becomes c * tanh(s / c), c the cap, before any bias; kept here as c / scale, so
+                         // that the capped value is a raw product again
   float softcap_in;      // scale / c: what the raw product is multiplied by inside the tanh
   const float* sinks;    // one per query head, or null: exp(sink) joins the softmax's denominator (no key, no value), once per row
   int shared_kv;         // the value tensor is the key tensor (vc == kc): a tile is fetched once and read as both
@@ -186,9 +187,12 @@ constexpr int BT_CACHE = 256;        // block-table entries a thread block keeps
 
 // Fetch keys [kt, kt+BN) of kv head hk into one stage of shared memory; keys outside [lo, hi) become zeros.
 // bt points at the table entry of block bt_first (shared memory copy, or the table itself with bt_first 0).
+template <bool SHARED>
 __device__ __forceinline__ void load_kv_tile(const Params& p, const int* bt, int bt_first, int hk, int kt, int lo, int hi, bf16* Ks,
                                              bf16* Vs) {
-  const int hkc = hk / p.kv_div;                 // the cached head this group of query heads reads
+  // the cached head this group of query heads reads (groups of a cached head exist only where keys are the values too)
+  const int hkc = SHARED ? hk / p.kv_div : hk;
+  const int cache_heads = SHARED ? p.cache_Hkv : p.Hkv;
 #pragma unroll
   for (int idx = threadIdx.x; idx < BN * CHUNKS; idx += THREADS) {
     const int row = idx / CHUNKS, ch = idx - row * CHUNKS;
@@ -199,10 +203,10 @@ __device__ __forceinline__ void load_kv_tile(const Params& p, const int* bt, int
       const int blk = p.ps_shift >= 0 ? (key >> p.ps_shift) : key / p.ps;
       const int page = blk < p.bt_width ? bt[blk - bt_first] : -1;
       ok = page >= 0 && page < p.num_pages;
-      if (ok) off = (((size_t)page * p.cache_Hkv + hkc) * p.ps + (key - blk * p.ps)) * D + ch * 8;
+      if (ok) off = (((size_t)page * cache_heads + hkc) * p.ps + (key - blk * p.ps)) * D + ch * 8;
     }
     cp_async16(Ks + row * LDS + ch * 8, p.kc + off, ok);
-    if (!p.shared_kv) cp_async16(Vs + row * LDS + ch * 8, p.vc + off, ok);
+    if (!SHARED) cp_async16(Vs + row * LDS + ch * 8, p.vc + off, ok);
   }
 }
 
@@ -226,6 +230,7 @@ __device__ __forceinline__ float ex2(float x) {
 // position (and inside every row's window) skip the mask; the heaviest row tiles (the last ones) start first.
 constexpr bool WQ_IN_REGS = D <= 128;
 
+template <bool SHARED>
 __global__ void __launch_bounds__(THREADS, (D <= 64 ? 4 : 1)) attention_wide_kernel(const Params p) {
   constexpr int BM = 64;
   constexpr int NT = BN / 8;
@@ -252,7 +257,7 @@ __global__ void __launch_bounds__(THREADS, (D <= 64 ? 4 : 1)) attention_wide_ker
   const int hi = p0 + row_last / G + 1;             // exclusive, <= L
   // keys every row of the tile may see without a mask (none with a distance bias or blocks of positions: every score
   // then goes through the masked path, which also takes the bias off)
-  const bool capped = p.softcap_log2 > 0.f;
+  const bool capped = p.cap_over_scale > 0.f;
   const bool by_distance = p.slopes != nullptr || p.chunk > 0 || capped;     // every score takes the masked path
   const int free_lo = by_distance ? 0x7fffffff : (p.window > 0 ? max(lo, p0 + row_last / G - p.window + 1) : lo);
   const int free_hi = by_distance ? 0 : min(hi, p0 + tok_first + 1);
@@ -279,8 +284,8 @@ __global__ void __launch_bounds__(THREADS, (D <= 64 ? 4 : 1)) attention_wide_ker
       bt_first = b_lo;
     }
   }
-  const int stage_elems = (p.shared_kv ? 1 : 2) * BN * LDS;     // keys that are the values too need no second tile
-  load_kv_tile(p, bt, bt_first, hk, kt0, lo, hi, KVs, KVs + BN * LDS);
+  constexpr int stage_elems = (SHARED ? 1 : 2) * BN * LDS;      // keys that are the values too need no second tile
+  load_kv_tile<SHARED>(p, bt, bt_first, hk, kt0, lo, hi, KVs, KVs + BN * LDS);
   cp_async_commit();
 
   const int row_a = m0 + warp * 16 + g, row_b = row_a + 8;
@@ -298,10 +303,10 @@ __global__ void __launch_bounds__(THREADS, (D <= 64 ? 4 : 1)) attention_wide_ker
   for (int it = 0; it < n_tiles; ++it) {
     const int kt = kt0 + it * BN;
     bf16* Ks = KVs + (it & 1) * stage_elems;
-    bf16* Vs = p.shared_kv ? Ks : Ks + BN * LDS;
+    bf16* Vs = SHARED ? Ks : Ks + BN * LDS;
     if (it + 1 < n_tiles) {
       bf16* Kn = KVs + ((it + 1) & 1) * stage_elems;
-      load_kv_tile(p, bt, bt_first, hk, kt + BN, lo, hi, Kn, Kn + BN * LDS);
+      load_kv_tile<SHARED>(p, bt, bt_first, hk, kt + BN, lo, hi, Kn, Kn + BN * LDS);
       cp_async_commit();
       cp_async_wait<1>();
     } else {
@@ -342,6 +347,13 @@ __global__ void __launch_bounds__(THREADS, (D <= 64 ? 4 : 1)) attention_wide_ker
         mx_b = fmaxf(mx_b, fmaxf(s[j][2], s[j][3]));
       }
     } else {
+      if (capped) {
+        // c tanh(s scale / c), left as a raw product again (divided by the scale) for the lines below to scale
+#pragma unroll
+        for (int j = 0; j < NT; ++j)
+#pragma unroll
+          for (int e = 0; e < 4; ++e) s[j][e] = p.cap_over_scale * tanh_fast(s[j][e] * p.softcap_in);
+      }
 #pragma unroll
       for (int j = 0; j < NT; ++j) {
 #pragma unroll
@@ -350,10 +362,8 @@ __global__ void __launch_bounds__(THREADS, (D <= 64 ? 4 : 1)) attention_wide_ker
           const bool in_range = key >= lo && key < hi;
           const bool ok_a = in_range && key <= pos_a && key >= first_a && (p.window <= 0 || key > pos_a - p.window);
           const bool ok_b = in_range && key <= pos_b && key >= first_b && (p.window <= 0 || key > pos_b - p.window);
-          const float va = capped ? p.softcap_log2 * tanh_fast(s[j][e] * p.softcap_in) : s[j][e] * p.scale_log2;
-          const float vb = capped ? p.softcap_log2 * tanh_fast(s[j][2 + e] * p.softcap_in) : s[j][2 + e] * p.scale_log2;
-          s[j][e] = ok_a ? va - slope_a * (float)(pos_a - key) : -INFINITY;
-          s[j][2 + e] = ok_b ? vb - slope_b * (float)(pos_b - key) : -INFINITY;
+          s[j][e] = ok_a ? s[j][e] * p.scale_log2 - slope_a * (float)(pos_a - key) : -INFINITY;
+          s[j][2 + e] = ok_b ? s[j][2 + e] * p.scale_log2 - slope_b * (float)(pos_b - key) : -INFINITY;
           mx_a = fmaxf(mx_a, s[j][e]);
           mx_b = fmaxf(mx_b, s[j][2 + e]);
         }
@@ -446,14 +456,17 @@ constexpr bool DQ_IN_REGS = D <= 128;                     // query fragments liv
 constexpr int DCOPIES = DKW * CHUNKS / 32;                // 16-byte copies per lane per sub-tile and tensor
 
 // Sub-tile of keys [k0, k0 + DKW) of kv head hk -> one stage. Keys outside [lo, hi) become zeros.
+template <bool SHARED>
 __device__ __forceinline__ void load_kv_subtile(const Params& p, const int* bt, int bt_first, int hk, int k0, int lo, int hi,
                                                 bool same_page, bf16* Ks, bf16* Vs, int lane) {
-  const int hkc = hk / p.kv_div;                 // the cached head this group of query heads reads
+  // the cached head this group of query heads reads (groups of a cached head exist only where keys are the values too)
+  const int hkc = SHARED ? hk / p.kv_div : hk;
+  const int cache_heads = SHARED ? p.cache_Hkv : p.Hkv;
   if (same_page) {
     const int blk = p.ps_shift >= 0 ? (k0 >> p.ps_shift) : k0 / p.ps;
     const int page = blk < p.bt_width ? bt[blk - bt_first] : -1;
     const bool page_ok = page >= 0 && page < p.num_pages;
-    const size_t base = (((size_t)(page_ok ? page : 0) * p.cache_Hkv + hkc) * p.ps + (k0 - blk * p.ps)) * D;
+    const size_t base = (((size_t)(page_ok ? page : 0) * cache_heads + hkc) * p.ps + (k0 - blk * p.ps)) * D;
     const bool inner = page_ok && k0 >= lo && k0 + DKW <= hi;
 #pragma unroll
     for (int i = 0; i < DCOPIES; ++i) {
@@ -461,7 +474,7 @@ __device__ __forceinline__ void load_kv_subtile(const Params& p, const int* bt, 
       const int row = c / CHUNKS, ch = c - row * CHUNKS;
       const bool ok = inner || (page_ok && k0 + row >= lo && k0 + row < hi);
       cp_async16(Ks + row * LDS + ch * 8, p.kc + base + (size_t)c * 8, ok);
-      if (!p.shared_kv) cp_async16(Vs + row * LDS + ch * 8, p.vc + base + (size_t)c * 8, ok);
+      if (!SHARED) cp_async16(Vs + row * LDS + ch * 8, p.vc + base + (size_t)c * 8, ok);
     }
     return;
   }
@@ -471,7 +484,7 @@ __device__ __forceinline__ void load_kv_subtile(const Params& p, const int* bt, 
     const int blk = k0 >> 4;
     const int page_a = blk < p.bt_width ? bt[blk - bt_first] : -1, page_b = blk + 1 < p.bt_width ? bt[blk + 1 - bt_first] : -1;
     const bool ok_a = page_a >= 0 && page_a < p.num_pages, ok_b = page_b >= 0 && page_b < p.num_pages;
-    const size_t base_a = ((size_t)(ok_a ? page_a : 0) * p.cache_Hkv + hkc) * 16 * D, base_b = ((size_t)(ok_b ? page_b : 0) * p.cache_Hkv + hkc) * 16 * D;
+    const size_t base_a = ((size_t)(ok_a ? page_a : 0) * cache_heads + hkc) * 16 * D, base_b = ((size_t)(ok_b ? page_b : 0) * cache_heads + hkc) * 16 * D;
     const bool inner = k0 >= lo && k0 + DKW <= hi;
 #pragma unroll
     for (int i = 0; i < DCOPIES; ++i) {
@@ -481,7 +494,7 @@ __device__ __forceinline__ void load_kv_subtile(const Params& p, const int* bt, 
       const bool ok = (second ? ok_b : ok_a) && (inner || (k0 + row >= lo && k0 + row < hi));
       const size_t off = (second ? base_b : base_a) + (size_t)(row & 15) * D + ch * 8;
       cp_async16(Ks + row * LDS + ch * 8, p.kc + off, ok);
-      if (!p.shared_kv) cp_async16(Vs + row * LDS + ch * 8, p.vc + off, ok);
+      if (!SHARED) cp_async16(Vs + row * LDS + ch * 8, p.vc + off, ok);
     }
     return;
   }
@@ -496,15 +509,16 @@ __device__ __forceinline__ void load_kv_subtile(const Params& p, const int* bt, 
       const int blk = p.ps_shift >= 0 ? (key >> p.ps_shift) : key / p.ps;
       const int page = blk < p.bt_width ? bt[blk - bt_first] : -1;
       ok = page >= 0 && page < p.num_pages;
-      if (ok) off = (((size_t)page * p.cache_Hkv + hkc) * p.ps + (key - blk * p.ps)) * D + ch * 8;
+      if (ok) off = (((size_t)page * cache_heads + hkc) * p.ps + (key - blk * p.ps)) * D + ch * 8;
     }
     cp_async16(Ks + row * LDS + ch * 8, p.kc + off, ok);
-    if (!p.shared_kv) cp_async16(Vs + row * LDS + ch * 8, p.vc + off, ok);
+    if (!SHARED) cp_async16(Vs + row * LDS + ch * 8, p.vc + off, ok);
   }
 }
 
 // NWARPS: 4 when many blocks share an SM, 8 when a block has an SM to itself (small batches).
-template <bool UPPER, int NWARPS>
+// OPTS: the launch has a distance bias, blocks of positions, a cap or sinks; without them that code is not compiled in.
+template <bool UPPER, int NWARPS, bool SHARED, bool OPTS>
 __global__ void __launch_bounds__(NWARPS * 32) attention_deep_kernel(const Params p) {
   constexpr int NTHR = NWARPS * 32;
   extern __shared__ __align__(16) unsigned char smem_raw[];
@@ -523,7 +537,7 @@ __global__ void __launch_bounds__(NWARPS * 32) attention_deep_kernel(const Param
   const int L = p.kv_len[r];
   const int p0 = L - qn;
   int lo = p.window > 0 ? max(0, p0 - p.window + 1) : 0;
-  if (p.chunk > 0) lo = max(lo, (p0 / p.chunk) * p.chunk);
+  if (OPTS && p.chunk > 0) lo = max(lo, (p0 / p.chunk) * p.chunk);
   int hi = p0 + (M - 1) / G + 1;
   {
     // the request's keys are shared out evenly over the launch's splits, in units of one step of all the block's
@@ -584,11 +598,11 @@ __global__ void __launch_bounds__(NWARPS * 32) attention_deep_kernel(const Param
   const int k_first = (lo / DKW) * DKW;
   const int n_sub = (hi - k_first + DKW - 1) / DKW;             // sub-tiles of the split
   const int my_n = (n_sub - warp + NWARPS - 1) / NWARPS;        // this warp's share: sub-tiles warp, warp+NWARPS, ...
-  const int stage_elems = (p.shared_kv ? 1 : 2) * DKW * LDS;    // keys that are the values too need no second sub-tile
+  constexpr int stage_elems = (SHARED ? 1 : 2) * DKW * LDS;     // keys that are the values too need no second sub-tile
   bf16* myKV = KVs + (size_t)warp * DSTAGES * stage_elems;
 #pragma unroll
   for (int s = 0; s < DSTAGES - 1; ++s) {
-    if (s < my_n) load_kv_subtile(p, bt, bt_first, hk, k_first + (warp + NWARPS * s) * DKW, lo, hi, same_page, myKV + s * stage_elems,
+    if (s < my_n) load_kv_subtile<SHARED>(p, bt, bt_first, hk, k_first + (warp + NWARPS * s) * DKW, lo, hi, same_page, myKV + s * stage_elems,
                                   myKV + s * stage_elems + DKW * LDS, lane);
     cp_async_commit();
   }
@@ -600,14 +614,14 @@ __global__ void __launch_bounds__(NWARPS * 32) attention_deep_kernel(const Param
   }
   const int pos_a = g < M ? p0 + g / G : -1;
   const int pos_b = (UPPER && g + 8 < M) ? p0 + (g + 8) / G : -1;
-  const float slope_a = (p.slopes && g < M) ? p.slopes[hk * G + g % G] * LOG2E : 0.f;
-  const float slope_b = (UPPER && p.slopes && g + 8 < M) ? p.slopes[hk * G + (g + 8) % G] * LOG2E : 0.f;
-  const int first_a = (p.chunk > 0 && pos_a >= 0) ? (pos_a / p.chunk) * p.chunk : 0;
-  const int first_b = (p.chunk > 0 && pos_b >= 0) ? (pos_b / p.chunk) * p.chunk : 0;
+  const float slope_a = (OPTS && p.slopes && g < M) ? p.slopes[hk * G + g % G] * LOG2E : 0.f;
+  const float slope_b = (OPTS && UPPER && p.slopes && g + 8 < M) ? p.slopes[hk * G + (g + 8) % G] * LOG2E : 0.f;
+  const int first_a = (OPTS && p.chunk > 0 && pos_a >= 0) ? (pos_a / p.chunk) * p.chunk : 0;
+  const int first_b = (OPTS && p.chunk > 0 && pos_b >= 0) ? (pos_b / p.chunk) * p.chunk : 0;
   // a sub-tile all of whose keys every row may see needs no mask: keys in [free_lo, free_hi) (none with a distance
   // bias or blocks of positions: the masked path takes the bias off)
-  const bool capped = p.softcap_log2 > 0.f;
-  const bool by_distance = p.slopes != nullptr || p.chunk > 0 || capped;     // every score takes the masked path
+  const bool capped = OPTS && p.cap_over_scale > 0.f;
+  const bool by_distance = OPTS && (p.slopes != nullptr || p.chunk > 0 || capped);     // every score takes the masked path
   const int free_lo = by_distance ? 0x7fffffff : max(lo, p.window > 0 ? p0 + (M - 1) / G - p.window + 1 : 0);
   const int free_hi = by_distance ? 0 : min(hi, p0 + 1);
   float o[D / 8][4];
@@ -620,14 +634,14 @@ __global__ void __launch_bounds__(NWARPS * 32) attention_deep_kernel(const Param
       const int nx = it + DSTAGES - 1;
       if (nx < my_n) {
         bf16* Kn = myKV + (nx % DSTAGES) * stage_elems;
-        load_kv_subtile(p, bt, bt_first, hk, k_first + (warp + NWARPS * nx) * DKW, lo, hi, same_page, Kn, Kn + DKW * LDS, lane);
+        load_kv_subtile<SHARED>(p, bt, bt_first, hk, k_first + (warp + NWARPS * nx) * DKW, lo, hi, same_page, Kn, Kn + DKW * LDS, lane);
       }
       cp_async_commit();
       cp_async_wait<DSTAGES - 1>();
     }
     __syncwarp();
     const bf16* Ks = myKV + (it % DSTAGES) * stage_elems;
-    const bf16* Vs = p.shared_kv ? Ks : Ks + DKW * LDS;
+    const bf16* Vs = SHARED ? Ks : Ks + DKW * LDS;
     const int kbase = k_first + (warp + NWARPS * it) * DKW;
     float s[DNT][4];
 #pragma unroll
@@ -662,6 +676,13 @@ __global__ void __launch_bounds__(NWARPS * 32) attention_deep_kernel(const Param
         }
       }
     } else {
+      if (capped) {
+        // c tanh(s scale / c), left as a raw product again (divided by the scale) for the lines below to scale
+#pragma unroll
+        for (int j = 0; j < DNT; ++j)
+#pragma unroll
+          for (int e = 0; e < (UPPER ? 4 : 2); ++e) s[j][e] = p.cap_over_scale * tanh_fast(s[j][e] * p.softcap_in);
+      }
 #pragma unroll
       for (int j = 0; j < DNT; ++j) {
 #pragma unroll
@@ -669,13 +690,11 @@ __global__ void __launch_bounds__(NWARPS * 32) attention_deep_kernel(const Param
           const int key = kbase + j * 8 + tq * 2 + e;
           const bool in_range = key >= lo && key < hi;
           const bool ok_a = in_range && key <= pos_a && key >= first_a && (p.window <= 0 || key > pos_a - p.window);
-          const float va = capped ? p.softcap_log2 * tanh_fast(s[j][e] * p.softcap_in) : s[j][e] * p.scale_log2;
-          s[j][e] = ok_a ? va - slope_a * (float)(pos_a - key) : -INFINITY;
+          s[j][e] = ok_a ? s[j][e] * p.scale_log2 - slope_a * (float)(pos_a - key) : -INFINITY;
           mx_a = fmaxf(mx_a, s[j][e]);
           if (UPPER) {
             const bool ok_b = in_range && key <= pos_b && key >= first_b && (p.window <= 0 || key > pos_b - p.window);
-            const float vb = capped ? p.softcap_log2 * tanh_fast(s[j][2 + e] * p.softcap_in) : s[j][2 + e] * p.scale_log2;
-            s[j][2 + e] = ok_b ? vb - slope_b * (float)(pos_b - key) : -INFINITY;
+            s[j][2 + e] = ok_b ? s[j][2 + e] * p.scale_log2 - slope_b * (float)(pos_b - key) : -INFINITY;
             mx_b = fmaxf(mx_b, s[j][2 + e]);
           }
         }
@@ -769,7 +788,7 @@ __global__ void __launch_bounds__(NWARPS * 32) attention_deep_kernel(const Param
       ll += MLm[(w * 16 + row) * 2 + 1] * f;
       acc += Om[((size_t)w * 16 + row) * D + d] * f;
     }
-    if (last && p.sinks != nullptr) {
+    if (OPTS && last && p.sinks != nullptr) {
       const float sk = p.sinks[hk * G + row % G] * LOG2E, mn = fmaxf(mm, sk);
       const float f = (mm == -INFINITY) ? 0.f : exp2f(mm - mn);
       ll = ll * f + exp2f(sk - mn);
@@ -795,8 +814,10 @@ size_t deep_smem_bytes(int nwarps, bool shared_kv = false) {
 
 template <bool UPPER, int NWARPS>
 int launch_deep(const Params& p, int n_rows, cudaStream_t stream) {
-  auto k = attention_deep_kernel<UPPER, NWARPS>;
   const size_t smem = deep_smem_bytes(NWARPS, p.shared_kv != 0);
+  const bool opts = p.slopes != nullptr || p.chunk > 0 || p.cap_over_scale > 0.f || p.sinks != nullptr;
+  auto k = p.shared_kv ? (opts ? attention_deep_kernel<UPPER, NWARPS, true, true> : attention_deep_kernel<UPPER, NWARPS, true, false>)
+                       : (opts ? attention_deep_kernel<UPPER, NWARPS, false, true> : attention_deep_kernel<UPPER, NWARPS, false, false>);
   if (smem > 48 * 1024) cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   SB_PDL_CHECK(launch_pdl(k, dim3(p.num_splits, p.Hkv, n_rows), dim3(NWARPS * 32), smem, stream, p));
   return 0;
@@ -837,7 +858,7 @@ SB_EXPORT int sb_attention_mma_opts(const void* qkv, int q_stride, const void* k
   if (n_rows <= 0 || max_q <= 0) return 0;
   if (H <= 0 || Hkv <= 0 || H % Hkv || ps <= 0 || bt_width <= 0) return SB_ERR_SHAPE;
   // Hkv counts the groups of query heads; the cache has Hkv / kv_div heads (kv_div 1: the usual case)
-  if (kv_div < 1 || Hkv % kv_div) return SB_ERR_SHAPE;
+  if (kv_div < 1 || Hkv % kv_div || (kv_div > 1 && kc != vc)) return SB_ERR_SHAPE;
   if (Hkv > 65535 || n_rows > 65535) return SB_ERR_LIMIT;
   if ((q_stride % 8) || !aligned16(qkv) || !aligned16(kc) || !aligned16(vc) || !aligned16(out)) return SB_ERR_ALIGN;
   Params p;
@@ -847,11 +868,11 @@ SB_EXPORT int sb_attention_mma_opts(const void* qkv, int q_stride, const void* k
   p.H = H; p.Hkv = Hkv; p.G = H / Hkv; p.ps = ps; p.num_pages = num_pages;
   p.ps_shift = (ps & (ps - 1)) == 0 ? __builtin_ctz((unsigned)ps) : -1;
   p.scale_log2 = scale * LOG2E; p.window = window; p.out = (bf16*)out; p.slopes = slopes; p.chunk = chunk;
-  p.softcap_log2 = softcap > 0.f ? softcap * LOG2E : 0.f; p.softcap_in = softcap > 0.f ? scale / softcap : 0.f; p.sinks = sinks; p.shared_kv = (kc == vc) ? 1 : 0;
+  p.cap_over_scale = softcap > 0.f ? softcap / scale : 0.f; p.softcap_in = softcap > 0.f ? scale / softcap : 0.f; p.sinks = sinks; p.shared_kv = (kc == vc) ? 1 : 0;
   p.split_size = 0; p.num_splits = num_splits; p.part_o = nullptr; p.part_ml = nullptr; p.tickets = nullptr;
   p.wide_rows = wide_rows; p.heads_in_x = 0;
   if (which & 1) {
-    auto k = attention_wide_kernel;
+    auto k = p.shared_kv ? attention_wide_kernel<true> : attention_wide_kernel<false>;
     const size_t smem = wide_smem_bytes(p.shared_kv != 0);
     if (smem > 48 * 1024) cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     const long long tiles = ((long long)max_q * p.G + 63) / 64;
@@ -988,7 +1009,7 @@ SB_EXPORT int sb_attention_decode_noalloc(const void* qkv, int q_stride, const v
   p.H = H; p.Hkv = Hkv; p.G = G; p.ps = ps; p.num_pages = num_pages;
   p.ps_shift = (ps & (ps - 1)) == 0 ? __builtin_ctz((unsigned)ps) : -1;
   p.scale_log2 = scale * LOG2E; p.window = window; p.out = (bf16*)out; p.slopes = nullptr; p.chunk = 0;
-  p.softcap_log2 = 0.f; p.softcap_in = 0.f; p.sinks = nullptr; p.shared_kv = (kc == vc) ? 1 : 0; p.cache_Hkv = Hkv; p.kv_div = 1;
+  p.cap_over_scale = 0.f; p.softcap_in = 0.f; p.sinks = nullptr; p.shared_kv = (kc == vc) ? 1 : 0; p.cache_Hkv = Hkv; p.kv_div = 1;
   p.split_size = 0; p.num_splits = num_splits; p.part_o = nullptr; p.part_ml = nullptr; p.tickets = nullptr;
   p.wide_rows = nullptr;
   if (num_splits > 1) {
